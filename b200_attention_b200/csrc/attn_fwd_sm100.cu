@@ -1,0 +1,935 @@
+// Dense, non-causal forward attention for sm_100a: O = softmax(Q K^T * scale) V, bf16 in,
+// bf16 out, fp32 accumulation, optional fp32 LSE, head_dim 128.
+//
+// Two kernels share the operand layout, descriptors and epilogue:
+//
+//   attn_fwd_ws_kernel      the production kernel. Persistent CTAs (one per SM), 16 warps:
+//                             warps 0-3   softmax for Q tile 0 (one query row per thread)
+//                             warps 4-7   softmax for Q tile 1
+//                             warps 8-11  correction: rescales the O accumulators when a row
+//                                         maximum moves, and runs the epilogue (normalise,
+//                                         merge with a previous partial, store O / LSE)
+//                             warp 12     issues every tcgen05.mma
+//                             warp 13     issues every TMA load
+//                             warps 14-15 only give their registers away
+//                           Q tiles, and a ring of K / V tiles, sit in 128-byte-swizzled shared
+//                           memory; S = Q K^T, the bf16 P that overwrites it, and both O
+//                           accumulators live in TMEM (4 x 128 columns).
+//
+//   attn_fwd_serial_kernel  bring-up / cross-check kernel: one CTA per 128 query rows, every
+//                           step serialised, exact rescale on every tile, all exponentials on
+//                           the MUFU unit. Used by the tests as an independent second opinion.
+//
+// Operand layout in shared memory (identical for Q, K and V): a 128 x 128 bf16 tile is two TMA
+// boxes of 64 columns x 128 rows, each row 128 bytes, 16-byte chunks XOR-swizzled by (row % 8).
+//   Q, K as K-major operands:  row = M/N index, 8-row groups 1024 bytes apart (SBO); a K step
+//                              of 16 elements is +32 bytes inside the row, steps 4..7 are in
+//                              the second box (+16 KiB).
+//   V as MN-major B operand:   row = K index (key), 8-key groups 1024 bytes apart (SBO), the
+//                              two 64-wide halves of head_dim 16 KiB apart (LBO); a K step of
+//                              16 keys is +2048 bytes.
+
+#include "attn_kernels.cuh"
+#include "ptx_sm100.cuh"
+
+#include <cfloat>
+#include <cmath>
+
+namespace b200attn {
+
+namespace {
+
+using namespace ptx;
+
+constexpr int kTileBytes = kBlockM * kHeadDim * 2;  // 32 KiB: one Q, K or V tile
+constexpr int kBoxBytes = kTileBytes / 2;           // one 64-column TMA box
+constexpr int kSwizzleGroupBytes = 1024;            // 8 rows x 128 bytes
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kNegInf = -INFINITY;
+
+constexpr uint32_t kIdescQK = umma_idesc_bf16(kBlockM, kBlockN, /*b_mn_major=*/false);
+constexpr uint32_t kIdescPV = umma_idesc_bf16(kBlockM, kHeadDim, /*b_mn_major=*/true);
+
+// ------------------------------------------------------------------------------------------
+// Bounded waits
+// ------------------------------------------------------------------------------------------
+struct WaitCtx {
+  uint32_t abort_addr;  // shared-memory word: non-zero once any thread of the CTA gave up
+  int32_t* status;
+  uint64_t limit_ns;
+  int32_t item;
+  int32_t tile;
+
+  __device__ __forceinline__ bool aborted() const {
+    uint32_t v;
+    asm volatile("ld.volatile.shared::cta.u32 %0, [%1];\n" : "=r"(v) : "r"(abort_addr));
+    return v != 0;
+  }
+
+  __device__ __forceinline__ void raise(int code, int site, uint32_t parity) const {
+    asm volatile("st.volatile.shared::cta.u32 [%0], %1;\n" ::"r"(abort_addr), "r"(1u) : "memory");
+    if (status != nullptr && atomicCAS(status, 0, code) == 0) {
+      status[1] = site;
+      status[2] = static_cast<int32_t>(blockIdx.x);
+      status[3] = static_cast<int32_t>(threadIdx.x >> 5);
+      status[4] = static_cast<int32_t>(parity);
+      status[5] = item;
+      status[6] = tile;
+      __threadfence_system();
+    }
+  }
+
+  __device__ __forceinline__ bool wait_slow(uint32_t bar, uint32_t parity, int site) const {
+    const uint64_t t0 = global_timer_ns();
+    for (uint32_t n = 1;; ++n) {
+      if (mbar_try_wait(bar, parity, 1000)) return true;
+      if ((n & 7u) == 0) {
+        if (aborted()) return false;
+        if (global_timer_ns() - t0 > limit_ns) {
+          raise(kDevWaitTimeout, site, parity);
+          return false;
+        }
+      }
+    }
+  }
+
+  // For roles run by a single thread.
+  __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, int site) const {
+    if (mbar_try_wait(bar, parity, 0)) return true;
+    return wait_slow(bar, parity, site);
+  }
+
+  // For roles run by whole warps: every lane returns the same answer, so the warp stays
+  // converged for the .sync.aligned TMEM instructions that follow.
+  __device__ __forceinline__ bool wait_warp(uint32_t bar, uint32_t parity, int site) const {
+    bool ok = mbar_try_wait(bar, parity, 0);
+    if (__all_sync(0xffffffffu, ok)) return true;
+    if (!ok) ok = wait_slow(bar, parity, site);
+    return __all_sync(0xffffffffu, ok);
+  }
+};
+
+// ------------------------------------------------------------------------------------------
+// MMA issue helpers (called by one thread)
+// ------------------------------------------------------------------------------------------
+// S[128 x 128] = Q_tile * K_tile^T, eight K=16 steps over head_dim.
+__device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint32_t q_smem, uint32_t k_smem) {
+  constexpr uint32_t hi = umma_desc_hi_sw128(kSwizzleGroupBytes);
+  const uint32_t a0 = umma_desc_lo(q_smem, 0);
+  const uint32_t b0 = umma_desc_lo(k_smem, 0);
+#pragma unroll
+  for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+    // the address field counts 16-byte units
+    const uint32_t off = uint32_t(((kk >> 2) * kBoxBytes + (kk & 3) * 32) >> 4);
+    umma_ss(s_tmem, a0 + off, hi, b0 + off, hi, kIdescQK, kk > 0 ? 1u : 0u);
+  }
+}
+
+// O[128 x 128] (+)= P[128 x keys kk_begin*16 .. kk_end*16) * V_tile[those keys, :]
+__device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint32_t v_smem,
+                                         int kk_begin, int kk_end, bool accumulate_first) {
+  constexpr uint32_t hi = umma_desc_hi_sw128(kSwizzleGroupBytes);
+  const uint32_t b0 = umma_desc_lo(v_smem, kBoxBytes);
+#pragma unroll
+  for (int kk = 0; kk < kBlockN / 16; ++kk) {
+    if (kk < kk_begin || kk >= kk_end) continue;
+    const uint32_t off = uint32_t((kk * 16 * 128) >> 4);
+    const uint32_t acc = (kk > kk_begin || accumulate_first) ? 1u : 0u;
+    umma_ts(o_tmem, p_tmem + kk * 8, b0 + off, hi, kIdescPV, acc);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Epilogue shared by both kernels: the calling thread owns one query row whose un-normalised
+// accumulator sits in TMEM lane `lane_of_row`, columns o_tmem .. o_tmem+127.
+// `after_last_ld` runs once, right after the final TMEM read has landed in registers.
+// ------------------------------------------------------------------------------------------
+struct RowOut {
+  bool valid;            // row < len_q
+  __nv_bfloat16* o_row;  // bf16 destination row (128 contiguous elements)
+  float* part_row;       // fp32 partial row, or nullptr
+  float w_cur;           // weight on this call's accumulator (includes 1 / rowsum)
+  float w_prev;          // weight on the stored partial (0 if none)
+  bool emit_partial;
+};
+
+__device__ __forceinline__ RowOut make_row_out(const FwdParams& p, int b, int h, int row, float m,
+                                               float l) {
+  RowOut r;
+  r.valid = row < p.len_q;
+  r.emit_partial = p.partial.emit != 0;
+  const int64_t flat = (int64_t(b) * p.heads + h) * p.len_q + row;
+  r.o_row = p.o + int64_t(b) * p.o_stride_b + int64_t(h) * p.o_stride_h +
+            int64_t(row) * p.o_stride_l;
+  r.part_row = (p.partial.o != nullptr) ? p.partial.o + flat * kHeadDim : nullptr;
+  const float inv_l = 1.0f / l;
+  float lse = (m + log2f(l)) * kLn2;
+  r.w_cur = inv_l;
+  r.w_prev = 0.0f;
+  if (r.valid) {
+    if (p.partial.merge != 0) {
+      const float lse_prev = p.partial.lse[flat];
+      const float top = fmaxf(lse_prev, lse);
+      const float lse_new = top + logf(expf(lse_prev - top) + expf(lse - top));
+      r.w_prev = expf(lse_prev - lse_new);
+      r.w_cur = expf(lse - lse_new) * inv_l;
+      lse = lse_new;
+    }
+    if (r.emit_partial) {
+      p.partial.lse[flat] = lse;
+    } else if (p.lse != nullptr) {
+      p.lse[flat] = lse;
+    }
+  }
+  return r;
+}
+
+template <class AfterLastLd>
+__device__ __forceinline__ void store_row(const RowOut& r, uint32_t o_tmem_row,
+                                          AfterLastLd after_last_ld) {
+  constexpr int kChunk = 16;  // columns per TMEM read: keeps the epilogue inside 80 registers
+#pragma unroll 1
+  for (int c = 0; c < kHeadDim / kChunk; ++c) {
+    uint32_t acc[kChunk];
+    tmem_ld16(o_tmem_row + c * kChunk, acc);
+    tmem_wait_ld();
+    if (c == kHeadDim / kChunk - 1) after_last_ld();
+    if (!r.valid) continue;
+    float v[kChunk];
+#pragma unroll
+    for (int j = 0; j < kChunk; ++j) v[j] = __uint_as_float(acc[j]) * r.w_cur;
+    if (r.w_prev != 0.0f) {
+      const float4* prev = reinterpret_cast<const float4*>(r.part_row + c * kChunk);
+#pragma unroll
+      for (int j = 0; j < kChunk / 4; ++j) {
+        const float4 t = prev[j];
+        v[4 * j + 0] = fmaf(t.x, r.w_prev, v[4 * j + 0]);
+        v[4 * j + 1] = fmaf(t.y, r.w_prev, v[4 * j + 1]);
+        v[4 * j + 2] = fmaf(t.z, r.w_prev, v[4 * j + 2]);
+        v[4 * j + 3] = fmaf(t.w, r.w_prev, v[4 * j + 3]);
+      }
+    }
+    if (r.emit_partial) {
+      float4* dst = reinterpret_cast<float4*>(r.part_row + c * kChunk);
+#pragma unroll
+      for (int j = 0; j < kChunk / 4; ++j)
+        dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {
+      uint4* dst = reinterpret_cast<uint4*>(r.o_row + c * kChunk);
+#pragma unroll
+      for (int j = 0; j < kChunk / 8; ++j) {
+        uint4 w;
+        w.x = pack_bf16x2(v[8 * j + 0], v[8 * j + 1]);
+        w.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+        w.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+        w.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+        dst[j] = w;
+      }
+    }
+  }
+}
+
+// Keys at or beyond `valid` (0 < valid < 128) do not exist: push their scores to -inf.
+__device__ __forceinline__ void mask_tail(uint32_t (&s)[4][32], int valid) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (c * 32 + j >= valid) s[c][j] = __float_as_uint(kNegInf);
+    }
+  }
+}
+
+__device__ __forceinline__ float row_max(const uint32_t (&s)[4][32]) {
+  float m0 = kNegInf, m1 = kNegInf, m2 = kNegInf, m3 = kNegInf;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      m0 = max3(m0, __uint_as_float(s[c][j + 0]), __uint_as_float(s[c][j + 1]));
+      m1 = max3(m1, __uint_as_float(s[c][j + 2]), __uint_as_float(s[c][j + 3]));
+      m2 = max3(m2, __uint_as_float(s[c][j + 4]), __uint_as_float(s[c][j + 5]));
+      m3 = max3(m3, __uint_as_float(s[c][j + 6]), __uint_as_float(s[c][j + 7]));
+    }
+  }
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+
+// ==========================================================================================
+// Warp-specialised persistent kernel
+// ==========================================================================================
+#ifndef B200ATTN_KV_STAGES
+#define B200ATTN_KV_STAGES 4
+#endif
+// Of every 16 exponentials, this many (taken from the end of each 16-column group) are
+// computed with the FMA-pipe polynomial instead of the MUFU unit.
+#ifndef B200ATTN_POLY_PER_16
+#define B200ATTN_POLY_PER_16 4
+#endif
+// A row keeps its old reference maximum until the true maximum has moved by at least this
+// many log2 units, so the O accumulator is rescaled rarely.
+#ifndef B200ATTN_RESCALE_THRESHOLD
+#define B200ATTN_RESCALE_THRESHOLD 8.0f
+#endif
+
+constexpr int kStages = B200ATTN_KV_STAGES;
+constexpr int kWsThreads = 512;
+constexpr int kRegsSoftmax = 192;
+constexpr int kRegsCorrection = 80;
+constexpr int kRegsOther = 48;
+
+enum WsBarrier : int {
+  kBarQFull = 0,    // +q   TMA -> MMA       Q tile q landed
+  kBarQEmpty = 2,   // +q   MMA -> TMA       last QK of the item that reads Q tile q finished
+  kBarSFull = 4,    // +q   MMA -> softmax   S_q holds the scores of the next tile
+  kBarPReady = 6,   // +q   softmax (4 warps) + correction (4 warps) -> MMA: P_q stored, O_q safe
+  kBarStats = 8,    // +q   softmax (4 warps) -> correction: rescale factors published
+  kBarPvDone = 10,  // +q   MMA -> correction: final PV of the item finished
+  kBarFin = 12,     // +q   softmax (4 warps) -> correction: final (max, sum) published
+  kBarFinFree = 14, // +q   correction (4 warps) -> softmax: final (max, sum) consumed
+  kBarDrain = 16,   //      MMA -> MMA       used only when leaving early
+  kBarKvFull = 18,  // +stage
+  kBarKvEmpty = 18 + kStages,
+  kNumWsBarriers = 18 + 2 * kStages
+};
+
+struct alignas(16) WsAux {
+  uint64_t bar[kNumWsBarriers];
+  float rescale[kQTilesPerItem][kBlockM];
+  float row_max[kQTilesPerItem][kBlockM];
+  float row_sum[kQTilesPerItem][kBlockM];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+constexpr int kWsSmemBytes = kQTilesPerItem * kTileBytes + kStages * kTileBytes + int(sizeof(WsAux));
+
+struct ItemCoord {
+  int b, h, row0;
+};
+
+__device__ __forceinline__ ItemCoord decode_item(const FwdParams& p, int item) {
+  ItemCoord c;
+  const int bh = item / p.m_blocks;
+  c.row0 = (item - bh * p.m_blocks) * kItemRows;
+  c.b = bh / p.heads;
+  c.h = bh - c.b * p.heads;
+  return c;
+}
+
+// ---- TMA producer -------------------------------------------------------------------------
+__device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, int row, int h,
+                                          int b, uint32_t bar) {
+  mbar_arrive_expect_tx(bar, kTileBytes);
+  tma_load_4d(dst, map, 0, row, h, b, bar);
+  tma_load_4d(dst + kBoxBytes, map, 64, row, h, b, bar);
+}
+
+__device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CUtensorMap* tk,
+                             const CUtensorMap* tv, uint32_t smem_q, uint32_t smem_kv,
+                             uint32_t bar0, WaitCtx& w) {
+  uint32_t stage = 0, empty_parity = 1;  // parity 1 passes on a fresh barrier
+  uint32_t q_empty_parity = 1;
+  // For the early-exit path: which "full" barriers were armed, and with which parity last.
+  uint32_t armed = 0, armed_parity = 0;
+  uint32_t q_full_parity = 0;
+  bool ok = true;
+
+  auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
+  auto push_kv = [&](const CUtensorMap* map, int row, int h, int b, int site) -> bool {
+    if (!w.wait(bar(kBarKvEmpty + stage), empty_parity, site)) return false;
+    const uint32_t full_parity = empty_parity ^ 1u;
+    armed |= 1u << stage;
+    armed_parity = (armed_parity & ~(1u << stage)) | (full_parity << stage);
+    load_tile(smem_kv + stage * kTileBytes, map, row, h, b, bar(kBarKvFull + stage));
+    if (++stage == kStages) {
+      stage = 0;
+      empty_parity ^= 1u;
+    }
+    return true;
+  };
+
+  for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
+    const ItemCoord c = decode_item(p, item);
+    w.item = item;
+    for (int q = 0; ok && q < kQTilesPerItem; ++q) {
+      ok = w.wait(bar(kBarQEmpty + q), q_empty_parity, 100 + q);
+      if (!ok) break;
+      armed |= 1u << (kStages + q);
+      armed_parity = (armed_parity & ~(1u << (kStages + q))) | (q_full_parity << (kStages + q));
+      load_tile(smem_q + q * kTileBytes, tq, c.row0 + q * kBlockM, c.h, c.b, bar(kBarQFull + q));
+      if (q == 0) ok = push_kv(tk, 0, c.h, c.b, 110);  // K_0 right behind Q_0
+    }
+    q_empty_parity ^= 1u;
+    q_full_parity ^= 1u;
+    for (int i = 0; ok && i < p.kv_tiles; ++i) {
+      w.tile = i;
+      if (i > 0) ok = push_kv(tk, i * kBlockN, c.h, c.b, 111);
+      if (ok) ok = push_kv(tv, i * kBlockN, c.h, c.b, 112);
+    }
+  }
+
+  if (!ok || w.aborted()) {
+    // Leaving early: wait (bounded) for every copy this thread still has in flight, so no
+    // TMA write lands in shared memory after the CTA is gone.
+    WaitCtx quiet = w;
+    quiet.status = nullptr;
+    for (int s = 0; s < kStages + kQTilesPerItem; ++s) {
+      if (!((armed >> s) & 1u)) continue;
+      const uint32_t b =
+          (s < kStages) ? bar(kBarKvFull + s) : bar(kBarQFull + (s - kStages));
+      const uint64_t t0 = global_timer_ns();
+      while (!mbar_try_wait(b, (armed_parity >> s) & 1u, 1000)) {
+        if (global_timer_ns() - t0 > quiet.limit_ns) break;
+      }
+    }
+  }
+}
+
+// ---- MMA issuer ---------------------------------------------------------------------------
+__device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_kv, uint32_t bar0,
+                            uint32_t tmem_base, WaitCtx& w) {
+  auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
+  uint32_t stage = 0, full_parity = 0;
+  uint32_t q_full_parity = 0;
+  uint32_t p_ready_parity[kQTilesPerItem] = {0, 0};
+  bool ok = true;
+
+  auto advance = [&]() {
+    if (++stage == kStages) {
+      stage = 0;
+      full_parity ^= 1u;
+    }
+  };
+  const int T = p.kv_tiles;
+
+  for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
+    w.item = item;
+    w.tile = 0;
+    // ---- tile 0 scores for both Q tiles
+    if (!(ok = w.wait(bar(kBarKvFull + stage), full_parity, 200))) break;
+    {
+      const uint32_t k_smem = smem_kv + stage * kTileBytes;
+      for (int q = 0; q < kQTilesPerItem; ++q) {
+        if (!(ok = w.wait(bar(kBarQFull + q), q_full_parity, 201 + q))) break;
+        tc_fence_after_sync();
+        issue_qk(tmem_base + q * kBlockN, smem_q + q * kTileBytes, k_smem);
+        umma_commit(bar(kBarSFull + q));
+        if (T == 1) umma_commit(bar(kBarQEmpty + q));
+      }
+      if (!ok) break;
+      umma_commit(bar(kBarKvEmpty + stage));
+      advance();
+    }
+    q_full_parity ^= 1u;
+
+    for (int i = 0; ok && i < T; ++i) {
+      w.tile = i;
+      if (!(ok = w.wait(bar(kBarKvFull + stage), full_parity, 210))) break;
+      const uint32_t v_stage = stage;
+      const uint32_t v_smem = smem_kv + v_stage * kTileBytes;
+      advance();
+      const bool has_next = (i + 1 < T);
+      for (int q = 0; q < kQTilesPerItem; ++q) {
+        const uint32_t s_tmem = tmem_base + q * kBlockN;
+        const uint32_t o_tmem = tmem_base + kQTilesPerItem * kBlockN + q * kHeadDim;
+        if (!(ok = w.wait(bar(kBarPReady + q), p_ready_parity[q], 220 + q))) break;
+        p_ready_parity[q] ^= 1u;
+        tc_fence_after_sync();
+        issue_pv(o_tmem, s_tmem, v_smem, 0, kBlockN / 16, /*accumulate_first=*/i > 0);
+        if (q == kQTilesPerItem - 1) umma_commit(bar(kBarKvEmpty + v_stage));
+        if (!has_next) {
+          umma_commit(bar(kBarPvDone + q));
+        } else {
+          if (q == 0) {
+            if (!(ok = w.wait(bar(kBarKvFull + stage), full_parity, 230))) break;
+            tc_fence_after_sync();
+          }
+          issue_qk(s_tmem, smem_q + q * kTileBytes, smem_kv + stage * kTileBytes);
+          umma_commit(bar(kBarSFull + q));
+          if (i + 2 == T) umma_commit(bar(kBarQEmpty + q));
+          if (q == kQTilesPerItem - 1) {
+            umma_commit(bar(kBarKvEmpty + stage));
+            advance();
+          }
+        }
+      }
+    }
+  }
+
+  if (!ok || w.aborted()) {
+    // Leaving early: make sure nothing this thread issued is still running before TMEM goes.
+    umma_commit(bar(kBarDrain));
+    const uint64_t t0 = global_timer_ns();
+    while (!mbar_try_wait(bar(kBarDrain), 0, 1000)) {
+      if (global_timer_ns() - t0 > w.limit_ns) break;
+    }
+  }
+}
+
+// ---- softmax: one query row per thread ---------------------------------------------------
+__device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, uint32_t tmem_base,
+                                int q, int warp_in_group, int lane, WaitCtx& w) {
+  auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
+  const uint32_t lane_field = uint32_t(warp_in_group * 32) << 16;
+  const uint32_t s_tmem = tmem_base + q * kBlockN + lane_field;
+  const uint32_t p_tmem = s_tmem;  // bf16 P overwrites S columns 0..63
+  const int r = warp_in_group * 32 + lane;
+  const float scale_log2 = p.scale_log2;
+  const f2 scale2 = f2_splat(scale_log2);
+  const int T = p.kv_tiles;
+  const int tail_valid = p.len_kv - (T - 1) * kBlockN;  // keys in the last tile, 1..128
+  uint32_t s_parity = 0;
+  uint32_t fin_free_parity = 1;  // passes on the fresh barrier: nothing to consume yet
+
+  for (int item = blockIdx.x; item < p.total_items; item += gridDim.x) {
+    w.item = item;
+    w.tile = 0;
+    // The correction warps must have consumed the previous item's final (max, sum) before this
+    // group publishes anything for the next item. Besides protecting the two shared-memory
+    // slots it keeps this group at most one phase ahead on kBarStats and kBarFin even when an
+    // item has a single K/V tile. It costs nothing: the scores of the next item cannot exist
+    // before the previous item's last PV has finished, which is what the epilogue waits for.
+    if (!w.wait_warp(bar(kBarFinFree + q), fin_free_parity, 310 + q)) return;
+    fin_free_parity ^= 1u;
+    float m = kNegInf;  // reference maximum, log2 units
+    float l = 0.0f;     // running sum of 2^(s - m)
+    for (int i = 0; i < T; ++i) {
+      w.tile = i;
+      if (!w.wait_warp(bar(kBarSFull + q), s_parity, 300 + q)) return;
+      s_parity ^= 1u;
+      tc_fence_after_sync();
+
+      uint32_t s[4][32];
+      tmem_ld32(s_tmem + 0, s[0]);
+      tmem_ld32(s_tmem + 32, s[1]);
+      tmem_ld32(s_tmem + 64, s[2]);
+      tmem_ld32(s_tmem + 96, s[3]);
+      tmem_wait_ld();
+      if (i == T - 1 && tail_valid < kBlockN) mask_tail(s, tail_valid);
+
+      const float tile_max = row_max(s) * scale_log2;
+      float rescale = 1.0f;
+      if (i == 0) {
+        m = tile_max;
+      } else {
+        const float m_new = fmaxf(m, tile_max);
+        if (m_new - m >= B200ATTN_RESCALE_THRESHOLD) {
+          rescale = ex2_approx(m - m_new);
+          l *= rescale;
+          m = m_new;
+        }
+      }
+      aux->rescale[q][r] = rescale;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(kBarStats + q));
+
+      const f2 neg_m2 = f2_splat(-m);
+      f2 sum_a = f2_splat(0.0f), sum_b = f2_splat(0.0f);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const f2 x = f2_fma(f2_make(__uint_as_float(s[c][2 * j]), __uint_as_float(s[c][2 * j + 1])),
+                              scale2, neg_m2);
+          f2 e;
+          if ((j & 7) >= 8 - B200ATTN_POLY_PER_16 / 2) {
+            e = exp2_poly(x);
+          } else {
+            float x0, x1;
+            f2_split(x, x0, x1);
+            e = f2_make(ex2_approx(x0), ex2_approx(x1));
+          }
+          if (j & 1) sum_b = f2_add(sum_b, e); else sum_a = f2_add(sum_a, e);
+          float e0, e1;
+          f2_split(e, e0, e1);
+          packed[j] = pack_bf16x2(e0, e1);
+        }
+        tmem_st16(p_tmem + c * 16, packed);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(kBarPReady + q));
+
+      float a0, a1;
+      f2_split(f2_add(sum_a, sum_b), a0, a1);
+      l += a0 + a1;
+    }
+    aux->row_max[q][r] = m;
+    aux->row_sum[q][r] = l;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(kBarFin + q));
+  }
+}
+
+// ---- correction + epilogue -----------------------------------------------------------------
+__device__ void ws_correction_role(const FwdParams& p, WsAux* aux, uint32_t bar0,
+                                   uint32_t tmem_base, int warp_in_group, int lane, WaitCtx& w) {
+  auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
+  const uint32_t lane_field = uint32_t(warp_in_group * 32) << 16;
+  const int r = warp_in_group * 32 + lane;
+  const int T = p.kv_tiles;
+  uint32_t stats_parity[kQTilesPerItem] = {0, 0};
+  uint32_t fin_parity = 0;
+
+  // Both O accumulators start out free: stand in for the "O safe" half of the first tile.
+  if (lane == 0) {
+    mbar_arrive(bar(kBarPReady + 0));
+    mbar_arrive(bar(kBarPReady + 1));
+  }
+
+  for (int item = blockIdx.x; item < p.total_items; item += gridDim.x) {
+    w.item = item;
+    for (int i = 0; i < T; ++i) {
+      w.tile = i;
+      for (int q = 0; q < kQTilesPerItem; ++q) {
+        if (!w.wait_warp(bar(kBarStats + q), stats_parity[q], 400 + q)) return;
+        stats_parity[q] ^= 1u;
+        if (i == 0) continue;  // tile 0 has nothing to rescale; its "O safe" vote was cast early
+        const float f = aux->rescale[q][r];
+        if (__any_sync(0xffffffffu, f != 1.0f)) {
+          // The scores of tile i exist, so PV of tile i-1 (issued earlier by the same thread)
+          // has finished: O_q is stable.
+          tc_fence_after_sync();
+          const uint32_t o_tmem = tmem_base + kQTilesPerItem * kBlockN + q * kHeadDim + lane_field;
+#pragma unroll 1
+          for (int c = 0; c < kHeadDim / 32; ++c) {
+            uint32_t lo[16], hi[16];
+            tmem_ld16(o_tmem + c * 32, lo);
+            tmem_ld16(o_tmem + c * 32 + 16, hi);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              lo[j] = __float_as_uint(__uint_as_float(lo[j]) * f);
+              hi[j] = __float_as_uint(__uint_as_float(hi[j]) * f);
+            }
+            tmem_st16(o_tmem + c * 32, lo);
+            tmem_st16(o_tmem + c * 32 + 16, hi);
+          }
+          tmem_wait_st();
+          tc_fence_before_sync();
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(kBarPReady + q));
+      }
+    }
+
+    const ItemCoord c = decode_item(p, item);
+    for (int q = 0; q < kQTilesPerItem; ++q) {
+      if (!w.wait_warp(bar(kBarFin + q), fin_parity, 410 + q)) return;
+      if (!w.wait_warp(bar(kBarPvDone + q), fin_parity, 420 + q)) return;
+      tc_fence_after_sync();
+      const float fin_m = aux->row_max[q][r];
+      const float fin_l = aux->row_sum[q][r];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(kBarFinFree + q));
+      const RowOut out = make_row_out(p, c.b, c.h, c.row0 + q * kBlockM + r, fin_m, fin_l);
+      const uint32_t o_tmem = tmem_base + kQTilesPerItem * kBlockN + q * kHeadDim + lane_field;
+      store_row(out, o_tmem, [&]() {
+        // O_q is in registers: the next item's first PV may overwrite it.
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(kBarPReady + q));
+      });
+    }
+    fin_parity ^= 1u;
+  }
+}
+
+__global__ void __launch_bounds__(kWsThreads, 1)
+attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                   const __grid_constant__ CUtensorMap tmap_k,
+                   const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const uint32_t smem_q = smem_u32(smem);
+  const uint32_t smem_kv = smem_q + kQTilesPerItem * kTileBytes;
+  WsAux* aux = reinterpret_cast<WsAux*>(smem + (kQTilesPerItem + kStages) * kTileBytes);
+  const uint32_t bar0 = smem_u32(&aux->bar[0]);
+
+  WaitCtx w;
+  w.abort_addr = smem_u32(&aux->abort_flag);
+  w.status = p.status;
+  w.limit_ns = uint64_t(p.wait_limit_ms) * 1000000ull;
+  w.item = -1;
+  w.tile = -1;
+
+  const bool misaligned = (smem_q & 1023u) != 0;  // uniform across the CTA
+  if (threadIdx.x == 0) {
+    aux->abort_flag = 0;
+    if (misaligned) {
+      w.raise(kDevSmemMisaligned, 1, 0);
+    } else {
+      for (int q = 0; q < kQTilesPerItem; ++q) {
+        mbar_init(bar0 + 8u * (kBarQFull + q), 1);
+        mbar_init(bar0 + 8u * (kBarQEmpty + q), 1);
+        mbar_init(bar0 + 8u * (kBarSFull + q), 1);
+        mbar_init(bar0 + 8u * (kBarPReady + q), 8);
+        mbar_init(bar0 + 8u * (kBarStats + q), 4);
+        mbar_init(bar0 + 8u * (kBarPvDone + q), 1);
+        mbar_init(bar0 + 8u * (kBarFin + q), 4);
+        mbar_init(bar0 + 8u * (kBarFinFree + q), 4);
+      }
+      mbar_init(bar0 + 8u * kBarDrain, 1);
+      mbar_init(bar0 + 8u * (kBarDrain + 1), 1);
+      for (int s = 0; s < kStages; ++s) {
+        mbar_init(bar0 + 8u * (kBarKvFull + s), 1);
+        mbar_init(bar0 + 8u * (kBarKvEmpty + s), 1);
+      }
+      mbar_init_fence();
+      fence_proxy_async_smem();
+    }
+  }
+  if (misaligned) return;
+  if (warp == 12) {
+    tmem_alloc(smem_u32(&aux->tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = aux->tmem_base;
+
+  if (warp < 8) {
+    reg_grow<kRegsSoftmax>();
+    ws_softmax_role(p, aux, bar0, tmem_base, warp >> 2, warp & 3, lane, w);
+  } else if (warp < 12) {
+    reg_shrink<kRegsCorrection>();
+    ws_correction_role(p, aux, bar0, tmem_base, warp & 3, lane, w);
+  } else {
+    reg_shrink<kRegsOther>();
+    if (warp == 12) {
+      if (lane == 0) ws_mma_role(p, smem_q, smem_kv, bar0, tmem_base, w);
+    } else if (warp == 13) {
+      if (lane == 0) {
+        tma_prefetch_desc(&tmap_q);
+        tma_prefetch_desc(&tmap_k);
+        tma_prefetch_desc(&tmap_v);
+        ws_load_role(p, &tmap_q, &tmap_k, &tmap_v, smem_q, smem_kv, bar0, w);
+      }
+    }
+    __syncwarp();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 12) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ==========================================================================================
+// Serial bring-up kernel: one CTA per 128 query rows, 4 warps, thread 0 issues TMA and MMA.
+// ==========================================================================================
+struct alignas(16) SerialAux {
+  uint64_t bar_q, bar_k, bar_v, bar_mma, bar_drain;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+constexpr int kSerialSmemBytes = 3 * kTileBytes + int(sizeof(SerialAux));
+
+__global__ void __launch_bounds__(128, 1)
+attn_fwd_serial_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                       const __grid_constant__ CUtensorMap tmap_k,
+                       const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_q = smem_u32(smem);
+  const uint32_t smem_k = smem_q + kTileBytes;
+  const uint32_t smem_v = smem_k + kTileBytes;
+  SerialAux* aux = reinterpret_cast<SerialAux*>(smem + 3 * kTileBytes);
+  const uint32_t bar_q = smem_u32(&aux->bar_q), bar_k = smem_u32(&aux->bar_k),
+                 bar_v = smem_u32(&aux->bar_v), bar_mma = smem_u32(&aux->bar_mma);
+
+  WaitCtx w;
+  w.abort_addr = smem_u32(&aux->abort_flag);
+  w.status = p.status;
+  w.limit_ns = uint64_t(p.wait_limit_ms) * 1000000ull;
+  w.item = int(blockIdx.x);
+  w.tile = -1;
+
+  const bool misaligned = (smem_q & 1023u) != 0;
+  if (threadIdx.x == 0) {
+    aux->abort_flag = 0;
+    if (misaligned) {
+      w.raise(kDevSmemMisaligned, 2, 0);
+    } else {
+      mbar_init(bar_q, 1);
+      mbar_init(bar_k, 1);
+      mbar_init(bar_v, 1);
+      mbar_init(bar_mma, 1);
+      mbar_init(smem_u32(&aux->bar_drain), 1);
+      mbar_init_fence();
+      fence_proxy_async_smem();
+    }
+  }
+  if (misaligned) return;
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&aux->tmem_base), 256);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = aux->tmem_base;
+  const uint32_t lane_field = uint32_t(warp * 32) << 16;
+  const uint32_t s_tmem = tmem_base + lane_field;          // S, then P in columns 0..63
+  const uint32_t o_tmem = tmem_base + kBlockN + lane_field;
+
+  // The serial kernel's m-blocks are single 128-row tiles.
+  const int m_tiles = (p.len_q + kBlockM - 1) / kBlockM;
+  const int bh = int(blockIdx.x) / m_tiles;
+  const int row0 = (int(blockIdx.x) - bh * m_tiles) * kBlockM;
+  const int b = bh / p.heads, h = bh - b * p.heads;
+  const int T = p.kv_tiles;
+  const int tail_valid = p.len_kv - (T - 1) * kBlockN;
+  const bool issuer = threadIdx.x == 0;
+
+  uint32_t kv_parity = 0, mma_parity = 0;
+  uint32_t armed_parity = 0;  // parity of the K/V phase armed most recently (issuer only)
+  float m = kNegInf, l = 0.0f;
+  bool ok = true;
+
+  if (issuer) load_tile(smem_q, &tmap_q, row0, h, b, bar_q);
+
+  for (int i = 0; i < T; ++i) {
+    w.tile = i;
+    if (issuer) {
+      load_tile(smem_k, &tmap_k, i * kBlockN, h, b, bar_k);
+      load_tile(smem_v, &tmap_v, i * kBlockN, h, b, bar_v);
+      armed_parity = kv_parity;
+      ok = (i > 0) || w.wait(bar_q, 0, 500);
+      ok = ok && w.wait(bar_k, kv_parity, 501);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_qk(tmem_base, smem_q, smem_k);
+      }
+      umma_commit(bar_mma);  // always commit so nobody is left waiting for a missing arrival
+    }
+    __syncwarp();
+    if (!w.wait_warp(bar_mma, mma_parity, 502)) break;
+    mma_parity ^= 1u;
+    tc_fence_after_sync();
+
+    uint32_t s[4][32];
+    tmem_ld32(s_tmem + 0, s[0]);
+    tmem_ld32(s_tmem + 32, s[1]);
+    tmem_ld32(s_tmem + 64, s[2]);
+    tmem_ld32(s_tmem + 96, s[3]);
+    tmem_wait_ld();
+    if (i == T - 1 && tail_valid < kBlockN) mask_tail(s, tail_valid);
+
+    const float m_new = fmaxf(m, row_max(s) * p.scale_log2);
+    if (i > 0) {
+      const float alpha = ex2_approx(m - m_new);
+      l *= alpha;
+#pragma unroll 1
+      for (int c = 0; c < kHeadDim / 32; ++c) {
+        uint32_t acc[32];
+        tmem_ld32(o_tmem + c * 32, acc);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] = __float_as_uint(__uint_as_float(acc[j]) * alpha);
+        tmem_st32(o_tmem + c * 32, acc);
+      }
+    }
+    m = m_new;
+    float sum = 0.0f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t packed[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float e0 = ex2_approx(fmaf(__uint_as_float(s[c][2 * j]), p.scale_log2, -m));
+        const float e1 = ex2_approx(fmaf(__uint_as_float(s[c][2 * j + 1]), p.scale_log2, -m));
+        sum += e0 + e1;
+        packed[j] = pack_bf16x2(e0, e1);
+      }
+      tmem_st16(s_tmem + c * 16, packed);
+    }
+    l += sum;
+    tmem_wait_st();
+    tc_fence_before_sync();
+    __syncthreads();
+
+    if (issuer) {
+      tc_fence_after_sync();
+      ok = w.wait(bar_v, kv_parity, 503);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_pv(tmem_base + kBlockN, tmem_base, smem_v, 0, kBlockN / 16, i > 0);
+      }
+      umma_commit(bar_mma);
+    }
+    kv_parity ^= 1u;
+    __syncwarp();
+    if (!w.wait_warp(bar_mma, mma_parity, 504)) break;
+    mma_parity ^= 1u;
+    tc_fence_after_sync();
+  }
+
+  if (!w.aborted()) {
+    const RowOut out = make_row_out(p, b, h, row0 + warp * 32 + lane, m, l);
+    store_row(out, o_tmem, []() {});
+  } else if (issuer) {
+    // Bounded drain of the copies and MMAs still in flight before shared memory and TMEM go.
+    const uint64_t t0 = global_timer_ns();
+    const uint32_t bar_drain = smem_u32(&aux->bar_drain);
+    umma_commit(bar_drain);
+    while (!(mbar_try_wait(bar_q, 0, 1000) && mbar_try_wait(bar_k, armed_parity, 1000) &&
+             mbar_try_wait(bar_v, armed_parity, 1000) && mbar_try_wait(bar_drain, 0, 1000))) {
+      if (global_timer_ns() - t0 > w.limit_ns) break;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------
+cudaError_t prepare_kernels() {
+  // The warp-specialised kernel re-partitions registers between its roles. A growing role
+  // blocks in hardware until the CTA's pool has room, so refuse to run unless the pool the
+  // launch reserves (registers per thread x 512 threads) covers what the roles ask for.
+  cudaFuncAttributes fa;
+  cudaError_t e = cudaFuncGetAttributes(&fa, attn_fwd_ws_kernel);
+  if (e != cudaSuccess) return e;
+  constexpr int kPoolNeeded = 128 * (2 * kRegsSoftmax + kRegsCorrection + kRegsOther);
+  if (fa.numRegs * kWsThreads < kPoolNeeded) return cudaErrorLaunchOutOfResources;
+  e = cudaFuncSetAttribute(attn_fwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kWsSmemBytes);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(attn_fwd_serial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              kSerialSmemBytes);
+}
+
+cudaError_t launch_fwd_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                          const FwdParams& p, int sm_count, cudaStream_t stream) {
+  const int grid = p.total_items < sm_count ? p.total_items : sm_count;
+  attn_fwd_ws_kernel<<<grid, kWsThreads, kWsSmemBytes, stream>>>(tq, tk, tv, p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fwd_serial(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                              const FwdParams& p, cudaStream_t stream) {
+  const int m_tiles = (p.len_q + kBlockM - 1) / kBlockM;
+  const int grid = p.batch * p.heads * m_tiles;
+  attn_fwd_serial_kernel<<<grid, 128, kSerialSmemBytes, stream>>>(tq, tk, tv, p);
+  return cudaGetLastError();
+}
+
+}  // namespace b200attn

@@ -1,0 +1,63 @@
+// Internal interface between the C-ABI layer and the sm_100a attention kernels.
+#pragma once
+
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+
+namespace b200attn {
+
+constexpr int kHeadDim = 128;      // only head_dim the kernels are written for
+constexpr int kBlockM = 128;       // query rows per Q tile (= TMEM lanes)
+constexpr int kBlockN = 128;       // keys per K/V tile
+constexpr int kQTilesPerItem = 2;  // a work item is two Q tiles that share every K/V tile
+constexpr int kItemRows = kBlockM * kQTilesPerItem;
+
+// Device-side watchdog record, 8 ints, written only when something went wrong.
+//   [0] code (0 = clean), [1] site id, [2] blockIdx.x, [3] warp, [4] barrier parity,
+//   [5] work item, [6] K/V tile, [7] reserved
+constexpr int kStatusInts = 8;
+
+enum DeviceCode : int32_t {
+  kDevOk = 0,
+  kDevWaitTimeout = 1,    // a bounded mbarrier wait ran out
+  kDevSmemMisaligned = 2  // dynamic shared memory base was not 1024-byte aligned
+};
+
+// Chaining calls over successive K/V shards (the sequence-parallel ring): every call
+// but the last leaves a *partial* result, a normalised fp32 O plus its natural-log LSE,
+// in caller-provided scratch; every call but the first merges the partial it finds
+// there with its own result in the epilogue, in registers:
+//   lse' = log(exp(lse_a) + exp(lse_b)),  O' = O_a * exp(lse_a - lse') + O_b * exp(lse_b - lse')
+struct PartialState {
+  float* o;        // [batch, heads, len_q, 128] fp32 contiguous, or nullptr
+  float* lse;      // [batch, heads, len_q]      fp32 contiguous, or nullptr
+  int32_t merge;   // 1: combine with the partial already stored in (o, lse)
+  int32_t emit;    // 1: store the (merged) partial to (o, lse) instead of the bf16 output
+};
+
+struct FwdParams {
+  __nv_bfloat16* o;
+  float* lse;  // [batch, heads, len_q] fp32 natural-log LSE, may be null
+  int64_t o_stride_b, o_stride_h, o_stride_l;  // in elements; innermost stride is 1
+  int32_t batch, heads, len_q, len_kv;
+  int32_t m_blocks;     // ceil(len_q / kItemRows)
+  int32_t kv_tiles;     // ceil(len_kv / kBlockN)
+  int32_t total_items;  // batch * heads * m_blocks
+  float scale_log2;     // softmax_scale * log2(e)
+  int32_t* status;      // kStatusInts ints the kernel can write (device or mapped host memory)
+  uint32_t wait_limit_ms;
+  PartialState partial;
+};
+
+// Launchers. Both return cudaGetLastError() of the launch.
+cudaError_t launch_fwd_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                          const FwdParams& p, int sm_count, cudaStream_t stream);
+cudaError_t launch_fwd_serial(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                              const FwdParams& p, cudaStream_t stream);
+
+// One-time per-device function attribute set-up (max dynamic shared memory).
+cudaError_t prepare_kernels();
+
+}  // namespace b200attn

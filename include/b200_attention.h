@@ -1,0 +1,128 @@
+/*
+ * b200_attention.h — C ABI of libb200attn.so: dense, non-causal, forward scaled-dot-product
+ * attention for NVIDIA B200 (sm_100a). bf16 Q/K/V in, bf16 O out, optional fp32 LSE,
+ * head_dim 128. Plain pointers and sizes only; no torch types. Every entry point returns
+ * a b200attn_status (0 = success) and never throws or aborts.
+ *
+ * Which entry point replaces which interface of the reference project
+ * (IaroslavElistratov/b200-attention, paths relative to its root):
+ *
+ *   b200attn_bhld_launch   the per-checkpoint launcher symbol bound by the benchmark
+ *                          registry's generated glue,
+ *                          `void <launch_symbol>(const nv_bfloat16* Q, K, V, nv_bfloat16* O,
+ *                          int batch_heads, int len_q, int len_kv, cudaStream_t)`
+ *                          (benchmarks/registry.py:272-282; implemented by
+ *                          kernels/5_minor/18_tma_l2_promotion.cu:1007-1059), which is also
+ *                          what the capstone op calls (capstone-project/kernel/binding.cpp:13-23).
+ *   b200attn_bshd_launch   the direct-BSHD launcher
+ *                          `attention_tcgen05_v18_bshd_launch(Q, K, V, O, batch, heads, len_q,
+ *                          len_kv, stream)` (benchmarks/benchmark_bshd.py:151-160;
+ *                          kernels/variants/18_tma_l2_promotion_bshd.cu:1076-1133).
+ *   b200attn_forward       superset of both: arbitrary (batch, head, row) strides, runtime
+ *                          softmax scale, LSE output, partial-result chaining for a
+ *                          sequence-parallel K/V ring. The reference has no counterpart for
+ *                          the extra arguments (its scale is fixed at 1/sqrt(128),
+ *                          18_tma_l2_promotion.cu:654, and it has no LSE or multi-GPU path).
+ */
+#ifndef B200_ATTENTION_H_
+#define B200_ATTENTION_H_
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define B200ATTN_API __attribute__((visibility("default")))
+#else
+#define B200ATTN_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum b200attn_status {
+  B200ATTN_OK = 0,
+  B200ATTN_ERR_INVALID_ARGUMENT = 1,  /* null pointer, non-positive size, bad stride, bad struct */
+  B200ATTN_ERR_UNSUPPORTED = 2,       /* head_dim != 128, sizes beyond the kernel's limits */
+  B200ATTN_ERR_ARCH = 3,              /* device is not compute capability 10.0 */
+  B200ATTN_ERR_CUDA = 4,              /* a CUDA runtime call failed; see b200attn_last_error */
+  B200ATTN_ERR_DRIVER = 5,            /* tensor-map encoding failed or driver entry point missing */
+  B200ATTN_ERR_DEVICE_TIMEOUT = 6,    /* a bounded device-side wait ran out (kernel left early) */
+  B200ATTN_ERR_DEVICE_FAULT = 7       /* device-side self check failed (e.g. misaligned smem) */
+} b200attn_status;
+
+enum { B200ATTN_KERNEL_WARP_SPECIALIZED = 0, B200ATTN_KERNEL_SERIAL = 1 };
+
+/* One operand: base pointer (device memory) and strides in ELEMENTS for the batch, head and
+ * row (sequence) axes. The head_dim axis is contiguous. Every stride times 2 bytes must be a
+ * multiple of 16 bytes and the base 16-byte aligned (TMA requirements). */
+typedef struct b200attn_operand {
+  const void* ptr;
+  int64_t stride_batch;
+  int64_t stride_head;
+  int64_t stride_row;
+} b200attn_operand;
+
+typedef struct b200attn_forward_args {
+  uint32_t struct_bytes; /* sizeof(b200attn_forward_args), checked */
+  int32_t batch, heads, len_q, len_kv, head_dim;
+  b200attn_operand q, k, v; /* bf16 */
+  b200attn_operand o;       /* bf16, written; ptr is cast to mutable */
+  float* lse;               /* [batch, heads, len_q] fp32 contiguous, natural log; may be NULL */
+  float softmax_scale;      /* <= 0 selects 1/sqrt(head_dim) */
+  int32_t kernel;           /* B200ATTN_KERNEL_* */
+  /* Partial-result chaining (sequence-parallel K/V ring). Scratch owned by the caller:
+   *   partial_o   [batch, heads, len_q, 128] fp32 contiguous
+   *   partial_lse [batch, heads, len_q]      fp32 contiguous
+   * partial_merge != 0: the epilogue merges the (O, LSE) pair already stored there with this
+   *                     call's result (in registers, no extra kernel);
+   * partial_emit  != 0: the (merged) pair is written back there instead of to o / lse. */
+  float* partial_o;
+  float* partial_lse;
+  int32_t partial_merge;
+  int32_t partial_emit;
+  void* stream; /* cudaStream_t; NULL = the legacy default stream */
+} b200attn_forward_args;
+
+/* Asynchronous on args->stream. The device that is current when the call is made is used. */
+B200ATTN_API int b200attn_forward(const b200attn_forward_args* args);
+
+/* Q [batch_heads, len_q, 128], K/V [batch_heads, len_kv, 128], O like Q; all contiguous bf16.
+ * Unlike the reference launcher there is no len_q % 256 / len_kv % 128 restriction. */
+B200ATTN_API int b200attn_bhld_launch(const void* q, const void* k, const void* v, void* o, int batch_heads,
+                         int len_q, int len_kv, void* stream);
+
+/* Q [batch, len_q, heads, 128], K/V [batch, len_kv, heads, 128], O like Q; contiguous bf16,
+ * read and written in place (no layout copies). */
+B200ATTN_API int b200attn_bshd_launch(const void* q, const void* k, const void* v, void* o, int batch,
+                         int heads, int len_q, int len_kv, void* stream);
+
+/* The kernels never spin without a limit: a wait that exceeds the limit makes the CTA record
+ * where it stopped and leave. After synchronising the stream(s) you launched on, call this to
+ * learn whether that happened on `device` (-1 = current). On a non-zero result `record`
+ * (8 ints, may be NULL) receives {code, site, block, warp, parity, item, tile, 0}; the record
+ * is cleared by the call. */
+B200ATTN_API int b200attn_device_check(int device, int32_t record[8]);
+
+/* Limit for device-side waits, milliseconds (default 2000). Applies to later launches. */
+B200ATTN_API int b200attn_set_wait_limit_ms(uint32_t ms);
+
+/* Number of kernels this library has launched in this process (all devices, all streams). */
+B200ATTN_API uint64_t b200attn_launch_count(void);
+
+/* Peer access for the sequence-parallel ring, one process per GPU:
+ * export a handle for device memory owned by this process / map a peer's handle. */
+B200ATTN_API int b200attn_ipc_export(const void* device_ptr, unsigned char handle[64]);
+B200ATTN_API int b200attn_ipc_open(const unsigned char handle[64], void** mapped_ptr);
+B200ATTN_API int b200attn_ipc_close(void* mapped_ptr);
+/* Copy `bytes` from a peer-mapped (or local) pointer into local memory on `stream`. */
+B200ATTN_API int b200attn_copy_async(void* dst_local, const void* src, uint64_t bytes, void* stream);
+
+B200ATTN_API const char* b200attn_status_string(int status);
+/* Message of the last failing call on this thread ("" if none). */
+B200ATTN_API const char* b200attn_last_error(void);
+B200ATTN_API const char* b200attn_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_ATTENTION_H_ */

@@ -1,0 +1,112 @@
+"""CPU tests of the C ABI: the library builds for sm_100a, loads, exports every symbol the
+header declares, and rejects bad arguments before touching a device. No compute here."""
+
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+
+from b200_attention_b200 import _native as N
+
+ROOT = Path(__file__).resolve().parents[1]
+HEADER = ROOT / "include" / "b200_attention.h"
+
+
+def declared_symbols():
+    text = HEADER.read_text()
+    return re.findall(r"B200ATTN_API\s+[\w\s\*]+?\b(b200attn_\w+)\s*\(", text)
+
+
+def test_header_and_binding_agree():
+    assert sorted(declared_symbols()) == sorted(N.EXPORTED_SYMBOLS)
+
+
+def test_library_exports_every_declared_symbol(native_built):
+    lib = C.CDLL(str(native_built["core"]))
+    for name in declared_symbols():
+        assert hasattr(lib, name), name
+
+
+def test_version_and_status_strings(native_built):
+    assert "sm_100a" in N.version()
+    lib = N.lib()
+    assert lib.b200attn_status_string(0) == b"ok"
+    for code in range(1, 8):
+        assert lib.b200attn_status_string(code) not in (b"ok", b"unknown status")
+    assert lib.b200attn_status_string(99) == b"unknown status"
+
+
+def test_struct_layout_matches_header(native_built):
+    # 6 x 4 bytes, 4 operands of 32 bytes, lse ptr, scale + kernel, 2 ptrs, 2 ints, stream
+    assert C.sizeof(N.Operand) == 32
+    assert C.sizeof(N.ForwardArgs) == 24 + 4 * 32 + 8 + 8 + 16 + 8 + 8
+
+
+def _args(**over):
+    a = N.ForwardArgs()
+    a.struct_bytes = C.sizeof(N.ForwardArgs)
+    a.batch, a.heads, a.len_q, a.len_kv, a.head_dim = 1, 1, 256, 256, 128
+    for name in ("q", "k", "v", "o"):
+        setattr(a, name, N.Operand(0x10000, 0, 256 * 128, 128))
+    for key, val in over.items():
+        setattr(a, key, val)
+    return a
+
+
+@pytest.mark.parametrize("over, status", [
+    (dict(struct_bytes=4), N.STATUS_INVALID_ARGUMENT),
+    (dict(head_dim=64), N.STATUS_UNSUPPORTED),
+    (dict(len_q=0), N.STATUS_INVALID_ARGUMENT),
+    (dict(len_kv=-5), N.STATUS_INVALID_ARGUMENT),
+    (dict(kernel=7), N.STATUS_INVALID_ARGUMENT),
+    (dict(q=N.Operand(0, 0, 256 * 128, 128)), N.STATUS_INVALID_ARGUMENT),       # null
+    (dict(k=N.Operand(0x10008, 0, 256 * 128, 128)), N.STATUS_INVALID_ARGUMENT),  # misaligned
+    (dict(v=N.Operand(0x10000, 0, 256 * 128, 132)), N.STATUS_INVALID_ARGUMENT),  # stride % 8
+    (dict(o=N.Operand(0x10000, 0, 256 * 128, 64)), N.STATUS_INVALID_ARGUMENT),   # stride < 128
+    (dict(partial_merge=1), N.STATUS_INVALID_ARGUMENT),                          # no scratch given
+    (dict(softmax_scale=float("nan")), N.STATUS_INVALID_ARGUMENT),
+])
+def test_argument_errors_come_back_as_status_codes(native_built, over, status):
+    a = _args(**over)
+    rc = N.lib().b200attn_forward(C.byref(a))
+    assert rc == status
+    assert N.lib().b200attn_last_error() != b""
+    with pytest.raises(N.B200AttnError) as info:
+        N.check(rc)
+    assert info.value.status == status
+
+
+def test_null_args(native_built):
+    assert N.lib().b200attn_forward(None) == N.STATUS_INVALID_ARGUMENT
+
+
+def test_wait_limit_bounds(native_built):
+    assert N.lib().b200attn_set_wait_limit_ms(0) == N.STATUS_INVALID_ARGUMENT
+    assert N.lib().b200attn_set_wait_limit_ms(2000) == N.STATUS_OK
+
+
+def test_device_check_before_any_launch_is_clean(native_built):
+    assert N.lib().b200attn_device_check(0, None) == N.STATUS_OK
+
+
+def test_torch_shim_registers_reference_op_names(native_built):
+    import torch
+
+    torch.ops.load_library(str(native_built["torch_ops"]))
+    ops = torch.ops.b200_attention_b200
+    for name in ("sdpa", "sdpa_bshd", "sdpa_lse", "device_check"):
+        assert hasattr(ops, name)
+    x = torch.zeros(1, 1, 256, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="must be CUDA tensors"):
+        ops.sdpa(x, x, x)
+
+
+def test_ops_refuse_cpu_tensors():
+    import torch
+
+    from b200_attention_b200 import ops
+
+    x = torch.zeros(1, 1, 256, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.attention(x, x, x)
