@@ -1,0 +1,413 @@
+#!/usr/bin/env python
+"""Attention-forward benchmark: TFLOPS = 4*B*H*Lq*Lk*D / time on synthetic inputs.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload main|...] [--impl reference]
+
+One process per GPU (torchrun sets RANK / LOCAL_RANK / WORLD_SIZE). A step is one pass of the
+attention kernel over one resident batch; every rank owns `batch` independent (batch, head)
+slices of the global problem (no data-path collective), so scaling is weak: the global batch
+is `batch * N`. Rank 0 prints one JSON line.
+
+    value          device-timed TFLOPS, whole job, inputs already in HBM
+    e2e            the same metric through the public API with host buffers: pinned host ->
+                   device copies of Q, K, V and the device -> host copy of O inside the timed
+                   region, every step
+    roofline       tensor-core roofline of the attention kernel: achieved TFLOP/s per launch
+                   (CUDA events on the launch stream) over the measured cuBLAS bf16 peak
+    cpu_baseline   torch SDPA (math backend, fp32) on the host cores over a bounded sample of the
+                   same workload; it is what the reference project checks its kernels against
+    k18_same_gpu   the reference project's final kernel, built unmodified into oracle/_ref/,
+                   timed on the same GPU and inputs (null when that library is absent)
+
+`--impl reference` times the CPU arm alone (rank 0 only) and prints the same line shape.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+HEAD_DIM = 128
+METRIC = "attention fwd TFLOPS & % of B200 BF16 tensor peak at 1/2/4/8 GPUs"
+
+# name -> per-GPU (batch, heads, len_q, len_kv, layout)
+WORKLOADS = {
+    "main": (4, 16, 8192, 8192, "bhld"),          # B=4 H=16 L=8192: the headline config
+    "main_bshd": (4, 16, 8192, 8192, "bshd"),
+    "l1k": (64, 16, 1024, 1024, "bhld"),
+    "l2k": (32, 16, 2048, 2048, "bhld"),
+    "l4k": (16, 16, 4096, 4096, "bhld"),
+    "l16k": (4, 16, 16384, 16384, "bhld"),
+    "l32k": (2, 16, 32768, 32768, "bhld"),
+    "dit_self": (1, 12, 32768, 32768, "bshd"),
+    "dit_cross": (1, 12, 32768, 512, "bshd"),
+    "smoke": (1, 4, 1024, 1024, "bhld"),
+}
+
+
+def flops(b, h, lq, lk):
+    return 4.0 * b * h * lq * lk * HEAD_DIM
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            d = json.loads(path.read_text())
+            return {"bf16_tflops": float(d["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", 0.0)),
+                    "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+        except Exception:
+            pass
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+                power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # keep the samples taken under load (upper half by power) for the median
+        if sm:
+            cut = statistics.median(power) if len(power) > 3 else 0.0
+            loaded = [c for c, w in zip(sm, power) if w >= cut] or sm
+        else:
+            loaded = []
+        return {"sm_mhz": statistics.median(loaded) if loaded else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def physical_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+# --------------------------------------------------------------------------------------------
+# CPU arm: the reference project's own check call, torch SDPA math backend in fp32
+# --------------------------------------------------------------------------------------------
+def cpu_sdpa_sample(b, h, lq, lk, budget_s: float, max_heads: int | None = None):
+    """Times torch SDPA (math, fp32, CPU) head by head on inputs of the workload's distribution
+    until `budget_s` is spent. Returns (tflops, heads_done, seconds, cores)."""
+    import torch
+
+    from oracle import sdpa_oracle as O
+
+    cores = torch.get_num_threads()
+    g = torch.Generator().manual_seed(0)
+    total = b * h if max_heads is None else min(b * h, max_heads)
+    # cap the rows of one timed slice so the fp32 score matrix stays below ~1 GiB
+    rows = min(lq, max(256, (1 << 28) // max(lk, 1)))
+    done_flops, heads, t_total = 0.0, 0, 0.0
+    q = torch.randn(1, 1, rows, HEAD_DIM, generator=g).to(torch.bfloat16)
+    k = torch.randn(1, 1, lk, HEAD_DIM, generator=g).to(torch.bfloat16)
+    v = torch.randn(1, 1, lk, HEAD_DIM, generator=g).to(torch.bfloat16)
+    O.sdpa_torch_math(q[:, :, :64], k, v)  # warm the thread pool
+    while heads < total and t_total < budget_s:
+        t0 = time.perf_counter()
+        for r0 in range(0, lq, rows):
+            O.sdpa_torch_math(q[:, :, : min(rows, lq - r0)], k, v)
+            if time.perf_counter() - t0 + t_total > 3 * budget_s:
+                break
+        dt = time.perf_counter() - t0
+        t_total += dt
+        done_flops += flops(1, 1, lq, lk)
+        heads += 1
+    return done_flops / t_total / 1e12, heads, t_total, cores
+
+
+def run_reference_arm(args, rank, world):
+    b, h, lq, lk, layout = WORKLOADS[args.workload]
+    if rank != 0:
+        return
+    per_step_budget = max(1.0, min(20.0, 90.0 / max(args.steps + args.warmup, 1)))
+    for _ in range(args.warmup):
+        cpu_sdpa_sample(b, h, lq, lk, budget_s=per_step_budget / 4, max_heads=1)
+    vals, heads_done, secs, cores = [], 0, 0.0, 0
+    for _ in range(args.steps):
+        tf, heads, t, cores = cpu_sdpa_sample(b, h, lq, lk, budget_s=per_step_budget)
+        vals.append(tf)
+        heads_done += heads
+        secs += t
+    value = statistics.mean(vals)
+    sample = (f"torch scaled_dot_product_attention, math backend, fp32, CPU, {heads_done} (batch, head) "
+              f"slices of Lq={lq} x Lk={lk} over {args.steps} steps, {secs:.1f} s, scaled by FLOPs")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": flops(b * world, h, lq, lk) / (value * 1e12) * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32",
+        "data": "synthetic", "config": workload_config(args.workload, world),
+        "cpu_baseline": {"value": value, "unit": "TFLOPS", "cores": cores, "kind": "reference",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(name, world):
+    b, h, lq, lk, layout = WORKLOADS[name]
+    return {"workload": f"{name}: dense non-causal attention forward, B={b} per GPU, H={h}, Lq={lq}, "
+                        f"Lk={lk}, D=128, bf16 N(0,1), scale 1/sqrt(128), layout {layout.upper()}",
+            "global_batch": b * world, "heads": h, "len_q": lq, "len_kv": lk, "head_dim": HEAD_DIM,
+            "layout": layout, "parallelism": f"(batch,head)-sharded x{world}, no collective",
+            "l2_policy": "inputs+outputs per step (Q,K,V,O) exceed the 126 MB L2; no flush"}
+
+
+# --------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------
+def run_ours(args, rank, local_rank, world):
+    import torch
+    import torch.distributed as dist
+
+    from b200_attention_b200 import _native, ops
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    b, h, lq, lk, layout = WORKLOADS[args.workload]
+    shape_q = (b, h, lq, HEAD_DIM) if layout == "bhld" else (b, lq, h, HEAD_DIM)
+    shape_k = (b, h, lk, HEAD_DIM) if layout == "bhld" else (b, lk, h, HEAD_DIM)
+
+    # host-side inputs (pinned) are the source for the e2e leg and for the resident copies
+    g = torch.Generator().manual_seed(1234 + rank)
+    q_h = torch.randn(shape_q, generator=g).to(torch.bfloat16).pin_memory()
+    k_h = torch.randn(shape_k, generator=g).to(torch.bfloat16).pin_memory()
+    v_h = torch.randn(shape_k, generator=g).to(torch.bfloat16).pin_memory()
+    o_h = torch.empty(shape_q, dtype=torch.bfloat16).pin_memory()
+    q, k, v = q_h.to(dev), k_h.to(dev), v_h.to(dev)
+    o = torch.empty_like(q)
+    stream = torch.cuda.current_stream(dev)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing
+    for _ in range(args.warmup):
+        ops.attention(q, k, v, layout=layout, out=o)
+    barrier()
+    _native.device_check()
+    launches0 = _native.launch_count()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    evs[0].record(stream)
+    for i in range(args.steps):
+        ops.attention(q, k, v, layout=layout, out=o)
+        evs[i + 1].record(stream)
+    barrier()
+    total_ms = evs[0].elapsed_time(evs[-1])
+    per_launch = [evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)]
+    launches = _native.launch_count() - launches0
+    _native.device_check()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = max_over_ranks(total_ms)
+    ms_per_step = total_ms / args.steps
+    step_flops_global = flops(b * world, h, lq, lk)
+    value = step_flops_global / (ms_per_step * 1e-3) / 1e12
+    kernel_ms = statistics.mean(per_launch)
+    achieved = flops(b, h, lq, lk) / (kernel_ms * 1e-3) / 1e12
+
+    # ---- end to end: host buffers in, host buffer out, through the public API
+    e2e_steps = max(2, min(args.steps, 5))
+
+    def e2e_step():
+        q.copy_(q_h, non_blocking=True)
+        k.copy_(k_h, non_blocking=True)
+        v.copy_(v_h, non_blocking=True)
+        ops.attention(q, k, v, layout=layout, out=o)
+        o_h.copy_(o, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
+    e2e_value = step_flops_global / (e2e_ms * 1e-3) / 1e12
+    in_bytes = (q_h.numel() + k_h.numel() + v_h.numel()) * 2
+    out_bytes = o_h.numel() * 2
+
+    # ---- the reference project's final kernel on the same GPU and inputs (rank 0, BHLD only)
+    k18 = None
+    if rank == 0 and not args.no_k18:
+        k18 = time_k18(torch, q, k, v, layout, args)
+    # ---- CPU baseline on a bounded sample (rank 0, single-GPU runs only)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        tf, heads, secs, cores = cpu_sdpa_sample(b, h, lq, lk, budget_s=args.cpu_budget)
+        cpu = {"value": tf, "unit": "TFLOPS", "cores": cores, "kind": "reference",
+               "sample": (f"torch scaled_dot_product_attention (math backend, fp32, CPU: the call the "
+                          f"reference checks its kernels against), {heads} of {b * h} (batch, head) "
+                          f"slices of this workload, {secs:.1f} s, scaled by FLOPs")}
+
+    if rank == 0:
+        peaks = measured_peaks()
+        traffic = None
+        tpath = ROOT / "profiles" / "traffic.json"
+        if tpath.exists():
+            try:
+                traffic = json.loads(tpath.read_text()).get(args.workload)
+            except Exception:
+                traffic = None
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": workload_config(args.workload, world),
+            "pct_of_bf16_peak": 100.0 * value / world / peaks["bf16_tflops"],
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+                         "frac_of_sustained_peak": (achieved / peaks["bf16_tflops_sustained"]
+                                                    if peaks["bf16_tflops_sustained"] else None),
+                         "peak_source": f"{peaks['source']} cuBLAS bf16 burst",
+                         "kernel_ms": kernel_ms, "traffic": traffic,
+                         "hbm_gbs_algorithmic": (in_bytes + out_bytes) / (kernel_ms * 1e-3) / 1e9},
+            "e2e": {"value": e2e_value, "unit": "TFLOPS", "h2d_bytes_per_step": in_bytes * world,
+                    "d2h_bytes_per_step": out_bytes * world, "ms_per_step": e2e_ms},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "cpu_baseline": cpu,
+            "k18_same_gpu": k18,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def time_k18(torch, q, k, v, layout, args):
+    try:
+        from oracle import native_refs as R
+    except Exception:
+        return None
+    fn = None
+    if layout == "bhld" and R.k18_available():
+        fn = R.k18_bhld
+    elif layout == "bshd" and (R.REF_DIR / "libk18_bshd_ref.so").exists():
+        fn = R.k18_bshd
+    lq = q.shape[2] if layout == "bhld" else q.shape[1]
+    lk = k.shape[2] if layout == "bhld" else k.shape[1]
+    if fn is None or lq % 256 or lk % 128:
+        return None
+    b, h = (q.shape[0], q.shape[1]) if layout == "bhld" else (q.shape[0], q.shape[2])
+    for _ in range(max(3, args.warmup)):
+        fn(q, k, v)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn(q, k, v)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    return {"tflops": flops(b, h, lq, lk) / (ms * 1e-3) / 1e12, "ms": ms,
+            "what": "reference final checkpoint kernel (18_tma_l2_promotion), unmodified, same GPU, "
+                    "includes its per-call tensor-map encoding"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="main", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-k18", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--cpu-budget", type=float, default=12.0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+    run_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()
