@@ -283,7 +283,7 @@ enum WsBarrier : int {
   kBarQEmpty = 2,   // +q   MMA -> TMA       last QK of the item that reads Q tile q finished
   kBarSFull = 4,    // +q   MMA -> softmax   S_q holds the scores of the next tile
   kBarPReady = 6,   // +q   softmax (4 warps) + correction (4 warps) -> MMA: P_q stored, O_q safe
-  kBarStats = 8,    // +q   softmax (4 warps) -> correction: rescale factors published
+  kBarStats = 8,    // +q   softmax (4 warps) -> correction: rescale factors of tile i >= 1 published
   kBarPvDone = 10,  // +q   MMA -> correction: final PV of the item finished
   kBarFin = 12,     // +q   softmax (4 warps) -> correction: final (max, sum) published
   kBarFinFree = 14, // +q   correction (4 warps) -> softmax: final (max, sum) consumed
@@ -520,9 +520,14 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
           m = m_new;
         }
       }
-      aux->rescale[q][r] = rescale;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(kBarStats + q));
+      if (i > 0) {
+        // Tile 0 publishes nothing: there is no accumulator to rescale yet, and the correction
+        // warps do not wait for it (they may still be in the previous item's epilogue, so a
+        // tile-0 phase could complete twice before they looked, and parity would alias).
+        aux->rescale[q][r] = rescale;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(kBarStats + q));
+      }
 
       const f2 neg_m2 = f2_splat(-m);
       f2 sum_a = f2_splat(0.0f), sum_b = f2_splat(0.0f);
@@ -582,12 +587,13 @@ __device__ void ws_correction_role(const FwdParams& p, WsAux* aux, uint32_t bar0
 
   for (int item = blockIdx.x; item < p.total_items; item += gridDim.x) {
     w.item = item;
-    for (int i = 0; i < T; ++i) {
+    // Tile 0 has nothing to rescale and its "O safe" vote was cast early (at kernel start, or
+    // by the previous item's epilogue), so the loop starts at tile 1.
+    for (int i = 1; i < T; ++i) {
       w.tile = i;
       for (int q = 0; q < kQTilesPerItem; ++q) {
         if (!w.wait_warp(bar(kBarStats + q), stats_parity[q], 400 + q)) return;
         stats_parity[q] ^= 1u;
-        if (i == 0) continue;  // tile 0 has nothing to rescale; its "O safe" vote was cast early
         const float f = aux->rescale[q][r];
         if (__any_sync(0xffffffffu, f != 1.0f)) {
           // The scores of tile i exist, so PV of tile i-1 (issued earlier by the same thread)
