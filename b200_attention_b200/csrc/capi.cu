@@ -3,6 +3,7 @@
 
 #include "../../include/b200_attention.h"
 #include "attn_kernels.cuh"
+#include "host_common.cuh"
 
 #include <atomic>
 #include <cmath>
@@ -11,12 +12,8 @@
 #include <mutex>
 #include <string>
 
-namespace {
-
-using namespace b200attn;
-
-constexpr int kMaxDevices = 64;
-constexpr const char* kVersion = "b200attn 0.1 (sm_100a)";
+namespace b200attn {
+namespace host {
 
 thread_local std::string g_last_error;
 std::atomic<uint64_t> g_launches{0};
@@ -32,6 +29,17 @@ int fail_cuda(const char* what, cudaError_t e) {
   (void)cudaGetLastError();
   return fail(B200ATTN_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
 }
+
+}  // namespace host
+}  // namespace b200attn
+
+namespace {
+
+using namespace b200attn;
+using namespace b200attn::host;
+
+constexpr int kMaxDevices = 64;
+constexpr const char* kVersion = "b200attn 0.1 (sm_100a)";
 
 // ---- driver entry point for tensor-map encoding (resolved at run time: no link against libcuda)
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -117,17 +125,16 @@ int get_device(int* device_out, DeviceState** st_out) {
   return B200ATTN_OK;
 }
 
+}  // namespace
+
+namespace b200attn {
+namespace host {
+
 // ---- tensor maps
-struct MapKey {
-  const void* ptr;
-  int64_t sb, sh, sl;
-  int32_t batch, heads, len;
-  int32_t device;
-  bool operator==(const MapKey& o) const {
-    return ptr == o.ptr && sb == o.sb && sh == o.sh && sl == o.sl && batch == o.batch &&
-           heads == o.heads && len == o.len && device == o.device;
-  }
-};
+static bool same_key(const MapKey& a, const MapKey& o) {
+  return a.ptr == o.ptr && a.sb == o.sb && a.sh == o.sh && a.sl == o.sl && a.batch == o.batch &&
+         a.heads == o.heads && a.len == o.len && a.device == o.device;
+}
 
 struct MapCache {
   static constexpr int kSlots = 96;
@@ -144,7 +151,7 @@ int make_tensor_map(const MapKey& key, CUtensorMap* out) {
   {
     std::lock_guard<std::mutex> lock(g_maps.mu);
     for (int i = 0; i < g_maps.used; ++i) {
-      if (g_maps.keys[i] == key) {
+      if (same_key(g_maps.keys[i], key)) {
         *out = g_maps.maps[i];
         return B200ATTN_OK;
       }
@@ -199,7 +206,8 @@ int check_operand(const char* name, const b200attn_operand& t, int32_t batch, in
   return B200ATTN_OK;
 }
 
-}  // namespace
+}  // namespace host
+}  // namespace b200attn
 
 extern "C" {
 
