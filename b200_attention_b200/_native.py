@@ -27,11 +27,14 @@ STATUS_DRIVER = 5
 STATUS_DEVICE_TIMEOUT = 6
 STATUS_DEVICE_FAULT = 7
 
+NOALLOC_MAX_ROWS = 16384
+
 # Every symbol include/b200_attention.h declares (the CPU tests check the library exports all).
 EXPORTED_SYMBOLS = (
     "b200attn_forward",
     "b200attn_bhld_launch",
     "b200attn_bshd_launch",
+    "b200attn_forward_kv_split_noalloc",
     "b200attn_device_check",
     "b200attn_set_wait_limit_ms",
     "b200attn_launch_count",
@@ -102,6 +105,8 @@ def lib() -> C.CDLL:
         handle.b200attn_bhld_launch.restype = C.c_int
         handle.b200attn_bshd_launch.argtypes = [C.c_void_p] * 4 + [C.c_int] * 4 + [C.c_void_p]
         handle.b200attn_bshd_launch.restype = C.c_int
+        handle.b200attn_forward_kv_split_noalloc.argtypes = [C.POINTER(ForwardArgs), C.c_int32]
+        handle.b200attn_forward_kv_split_noalloc.restype = C.c_int
         handle.b200attn_device_check.argtypes = [C.c_int, C.POINTER(C.c_int32)]
         handle.b200attn_device_check.restype = C.c_int
         handle.b200attn_set_wait_limit_ms.argtypes = [C.c_uint32]

@@ -24,8 +24,9 @@ LIB = PKG / "lib"
 INCLUDE = PKG.parent / "include"
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
-CORE_SOURCES = [CSRC / "attn_fwd_sm100.cu", CSRC / "capi.cu"]
-CORE_HEADERS = [CSRC / "attn_kernels.cuh", CSRC / "ptx_sm100.cuh", INCLUDE / "b200_attention.h"]
+CORE_SOURCES = [CSRC / "attn_fwd_sm100.cu", CSRC / "capi.cu", CSRC / "noalloc.cu"]
+CORE_HEADERS = [CSRC / "attn_kernels.cuh", CSRC / "ptx_sm100.cuh", CSRC / "host_common.cuh",
+                INCLUDE / "b200_attention.h"]
 
 
 def _nvcc() -> str:

@@ -117,6 +117,23 @@ B200ATTN_API int b200attn_ipc_close(void* mapped_ptr);
 /* Copy `bytes` from a peer-mapped (or local) pointer into local memory on `stream`. */
 B200ATTN_API int b200attn_copy_async(void* dst_local, const void* src, uint64_t bytes, void* stream);
 
+/* Forward pass for callers that must not allocate (no counterpart in the reference project).
+ * Same arguments as b200attn_forward with partial_* unset; the key/value sequence is processed
+ * in up to `kv_splits` chunks of whole 128-key tiles whose (O, LSE) partials are chained through
+ * a fixed device array built into the library instead of caller scratch, and the wait watchdog
+ * record lives there too, so neither this call nor its first-use set-up calls cudaMalloc,
+ * cudaHostAlloc or any other allocating routine.
+ *   - Limit: batch * heads * len_q <= B200ATTN_NOALLOC_MAX_ROWS query rows (the array is
+ *     8,454,400 bytes and every GPU that loads the library holds it until process exit);
+ *     larger problems return B200ATTN_ERR_UNSUPPORTED.
+ *   - The first call on a device looks up the array's device address and sets kernel
+ *     attributes; make that call before any stream capture.
+ *   - All calls on a device share the array: calls whose kernels overlap on the GPU race.
+ *   - A device-side wait that ran out is reported by the next call that finds the stream idle;
+ *     kv_splits == 0 launches nothing and only performs that check (synchronise first). */
+#define B200ATTN_NOALLOC_MAX_ROWS 16384
+B200ATTN_API int b200attn_forward_kv_split_noalloc(const b200attn_forward_args* args, int32_t kv_splits);
+
 B200ATTN_API const char* b200attn_status_string(int status);
 /* Message of the last failing call on this thread ("" if none). */
 B200ATTN_API const char* b200attn_last_error(void);
