@@ -50,10 +50,37 @@ constexpr float kNegInf = -INFINITY;
 constexpr uint32_t kIdescQK = umma_idesc_bf16(kBlockM, kBlockN, /*b_mn_major=*/false);
 constexpr uint32_t kIdescPV = umma_idesc_bf16(kBlockM, kHeadDim, /*b_mn_major=*/true);
 
+// Timeline instrumentation, compiled in only for B200ATTN_TRACE builds: block 0 records clock64 at
+// fixed points of its first work item, for tiles [kTraceTile0, kTraceTile0 + kTraceTiles).
+// Layout: trace[((role * kTraceTiles + tile) * 2 + q) * 8 + event].
+#ifdef B200ATTN_TRACE
+constexpr int kTraceTile0 = 8, kTraceTiles = 16;
+#define B200ATTN_TRACE_EVENT(p, role, item, tile, q, ev)                                          \
+  do {                                                                                            \
+    if ((p).trace != nullptr && blockIdx.x == 0 && (item) == 0 && (tile) >= kTraceTile0 &&        \
+        (tile) < kTraceTile0 + kTraceTiles)                                                       \
+      (p).trace[(((role) * kTraceTiles + ((tile) - kTraceTile0)) * 2 + (q)) * 8 + (ev)] = clock64(); \
+  } while (0)
+// Same, but the clock is read only after `dep` (a float) has been computed.
+#define B200ATTN_TRACE_EVENT_AFTER(p, role, item, tile, q, ev, dep)                               \
+  do {                                                                                            \
+    if ((p).trace != nullptr && blockIdx.x == 0 && (item) == 0 && (tile) >= kTraceTile0 &&        \
+        (tile) < kTraceTile0 + kTraceTiles) {                                                     \
+      long long t_;                                                                               \
+      asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_) : "f"(dep));                               \
+      (p).trace[(((role) * kTraceTiles + ((tile) - kTraceTile0)) * 2 + (q)) * 8 + (ev)] = t_;     \
+    }                                                                                             \
+  } while (0)
+#else
+#define B200ATTN_TRACE_EVENT(p, role, item, tile, q, ev) do { } while (0)
+#define B200ATTN_TRACE_EVENT_AFTER(p, role, item, tile, q, ev, dep) do { } while (0)
+#endif
+
 // ------------------------------------------------------------------------------------------
 // Bounded waits
 // ------------------------------------------------------------------------------------------
 struct WaitCtx {
+  bool relaxed = false;  // role whose wake-up latency does not matter (may back off between polls)
   uint32_t abort_addr;  // shared-memory word: non-zero once any thread of the CTA gave up
   int32_t* status;
   uint64_t limit_ns;
@@ -83,6 +110,9 @@ struct WaitCtx {
     const uint64_t t0 = global_timer_ns();
     for (uint32_t n = 1;; ++n) {
       if (mbar_try_wait(bar, parity, 1000)) return true;
+#ifdef B200ATTN_SPIN_SLEEP
+      if (relaxed) __nanosleep(B200ATTN_SPIN_SLEEP);
+#endif
       if ((n & 7u) == 0) {
         if (aborted()) return false;
         if (global_timer_ns() - t0 > limit_ns) {
@@ -112,8 +142,10 @@ struct WaitCtx {
 // ------------------------------------------------------------------------------------------
 // MMA issue helpers (called by one thread)
 // ------------------------------------------------------------------------------------------
-// S[128 x 128] = Q_tile * K_tile^T, eight K=16 steps over head_dim.
-__device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint32_t q_smem, uint32_t k_smem) {
+// S[128 x 128] = Q_tile * K_tile^T, eight K=16 steps over head_dim. Executed by a whole warp with
+// uniform operands; only the lane with lead != 0 issues.
+__device__ __forceinline__ void issue_qk(uint32_t lead, uint32_t s_tmem, uint32_t q_smem,
+                                         uint32_t k_smem) {
   constexpr uint32_t hi = umma_desc_hi_sw128(kSwizzleGroupBytes);
   const uint32_t a0 = umma_desc_lo(q_smem, 0);
   const uint32_t b0 = umma_desc_lo(k_smem, 0);
@@ -121,13 +153,15 @@ __device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint32_t q_smem, uint3
   for (int kk = 0; kk < kHeadDim / 16; ++kk) {
     // the address field counts 16-byte units
     const uint32_t off = uint32_t(((kk >> 2) * kBoxBytes + (kk & 3) * 32) >> 4);
-    umma_ss(s_tmem, a0 + off, hi, b0 + off, hi, kIdescQK, kk > 0 ? 1u : 0u);
+    umma_ss_lead(lead, s_tmem, a0 + off, hi, b0 + off, hi, kIdescQK, kk > 0 ? 1u : 0u);
   }
 }
 
-// O[128 x 128] (+)= P[128 x keys kk_begin*16 .. kk_end*16) * V_tile[those keys, :]
-__device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint32_t v_smem,
-                                         int kk_begin, int kk_end, bool accumulate_first) {
+// O[128 x 128] (+)= P[128 x 128 keys] * V_tile, K steps [kk_begin, kk_end). P is bf16 pairs in
+// TMEM, 8 columns per K step starting at p_tmem.
+__device__ __forceinline__ void issue_pv(uint32_t lead, uint32_t o_tmem, uint32_t p_tmem,
+                                         uint32_t v_smem, int kk_begin, int kk_end,
+                                         bool accumulate_first) {
   constexpr uint32_t hi = umma_desc_hi_sw128(kSwizzleGroupBytes);
   const uint32_t b0 = umma_desc_lo(v_smem, kBoxBytes);
 #pragma unroll
@@ -135,7 +169,7 @@ __device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint3
     if (kk < kk_begin || kk >= kk_end) continue;
     const uint32_t off = uint32_t((kk * 16 * 128) >> 4);
     const uint32_t acc = (kk > kk_begin || accumulate_first) ? 1u : 0u;
-    umma_ts(o_tmem, p_tmem + kk * 8, b0 + off, hi, kIdescPV, acc);
+    umma_ts_lead(lead, o_tmem, p_tmem + kk * 8, b0 + off, hi, kIdescPV, acc);
   }
 }
 
@@ -241,6 +275,17 @@ __device__ __forceinline__ void mask_tail(uint32_t (&s)[4][32], int valid) {
 }
 
 __device__ __forceinline__ float row_max(const uint32_t (&s)[4][32]) {
+#ifdef B200ATTN_MAX2
+  float v[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) v[k] = kNegInf;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j & 7] = fmaxf(v[j & 7], __uint_as_float(s[c][j]));
+  }
+  return fmaxf(fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3])), fmaxf(fmaxf(v[4], v[5]), fmaxf(v[6], v[7])));
+#endif
   float m0 = kNegInf, m1 = kNegInf, m2 = kNegInf, m3 = kNegInf;
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
@@ -261,41 +306,48 @@ __device__ __forceinline__ float row_max(const uint32_t (&s)[4][32]) {
 #ifndef B200ATTN_KV_STAGES
 #define B200ATTN_KV_STAGES 4
 #endif
-// Of every 16 exponentials, this many (taken from the end of each 16-column group) are
-// computed with the FMA-pipe polynomial instead of the MUFU unit.
+// Of every 16 exponentials, this many are computed with the FMA-pipe polynomial instead of the
+// MUFU unit. 0 is fastest while the softmax warps are bound by instruction issue rather than by
+// MUFU throughput (measured: 0 -> 1282, 4 -> 1237, 8 -> 1140 TFLOPS at B4 H16 L8192).
 #ifndef B200ATTN_POLY_PER_16
-#define B200ATTN_POLY_PER_16 4
+#define B200ATTN_POLY_PER_16 0
 #endif
-// A row keeps its old reference maximum until the true maximum has moved by at least this
-// many log2 units, so the O accumulator is rescaled rarely.
-#ifndef B200ATTN_RESCALE_THRESHOLD
-#define B200ATTN_RESCALE_THRESHOLD 8.0f
+// A row keeps its reference maximum m until some score exceeds m by this many log2 units.
+// With bf16 probabilities and fp32 sums nothing overflows or loses relative precision until the
+// excess nears 2^100, so the bound can be generous; 32 makes a rebase a once-in-a-blue-moon event
+// on real data while leaving 2^(127-32-20) of headroom for row sums over a million keys.
+#ifndef B200ATTN_REBASE_LOG2
+#define B200ATTN_REBASE_LOG2 32.0f
 #endif
+// Number of leading 32-column chunks whose probabilities are published first ("part A"); the PV
+// MMAs over those keys start while the softmax warps still work on the rest ("part B").
+constexpr int kPartAChunks = 3;
+constexpr int kPartAKSteps = kPartAChunks * 2;  // K = 16 keys per MMA step
 
 constexpr int kStages = B200ATTN_KV_STAGES;
 constexpr int kWsThreads = 512;
 constexpr int kRegsSoftmax = 192;
-constexpr int kRegsCorrection = 80;
+constexpr int kRegsEpilogue = 80;
 constexpr int kRegsOther = 48;
 
 enum WsBarrier : int {
   kBarQFull = 0,    // +q   TMA -> MMA       Q tile q landed
   kBarQEmpty = 2,   // +q   MMA -> TMA       last QK of the item that reads Q tile q finished
   kBarSFull = 4,    // +q   MMA -> softmax   S_q holds the scores of the next tile
-  kBarPReady = 6,   // +q   softmax (4 warps) + correction (4 warps) -> MMA: P_q stored, O_q safe
-  kBarStats = 8,    // +q   softmax (4 warps) -> correction: rescale factors of tile i >= 1 published
-  kBarPvDone = 10,  // +q   MMA -> correction: final PV of the item finished
-  kBarFin = 12,     // +q   softmax (4 warps) -> correction: final (max, sum) published
-  kBarFinFree = 14, // +q   correction (4 warps) -> softmax: final (max, sum) consumed
-  kBarDrain = 16,   //      MMA -> MMA       used only when leaving early
-  kBarKvFull = 18,  // +stage
-  kBarKvEmpty = 18 + kStages,
-  kNumWsBarriers = 18 + 2 * kStages
+  kBarPReady = 6,   // +q   softmax (4 warps) -> MMA: part A of P_q stored (and O_q rebased if needed)
+  kBarPFull = 8,    // +q   softmax (4 warps) -> MMA: part B of P_q stored
+  kBarPvDone = 10,  // +q   MMA -> epilogue: final PV of the item finished
+  kBarFin = 12,     // +q   softmax (4 warps) -> epilogue: final (max, sum) published
+  kBarFinFree = 14, // +q   epilogue (4 warps) -> softmax: final (max, sum) consumed
+  kBarOFree = 16,   // +q   epilogue (4 warps) -> MMA: O_q read out, the next item may overwrite it
+  kBarDrain = 18,   //      MMA -> MMA       used only when leaving early
+  kBarKvFull = 20,  // +stage
+  kBarKvEmpty = 20 + kStages,
+  kNumWsBarriers = 20 + 2 * kStages
 };
 
 struct alignas(16) WsAux {
   uint64_t bar[kNumWsBarriers];
-  float rescale[kQTilesPerItem][kBlockM];
   float row_max[kQTilesPerItem][kBlockM];
   float row_sum[kQTilesPerItem][kBlockM];
   uint32_t tmem_base;
@@ -318,16 +370,17 @@ __device__ __forceinline__ ItemCoord decode_item(const FwdParams& p, int item) {
 }
 
 // ---- TMA producer -------------------------------------------------------------------------
-__device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, int row, int h,
-                                          int b, uint32_t bar) {
-  mbar_arrive_expect_tx(bar, kTileBytes);
-  tma_load_4d(dst, map, 0, row, h, b, bar);
-  tma_load_4d(dst + kBoxBytes, map, 64, row, h, b, bar);
+__device__ __forceinline__ void load_tile(uint32_t lead, uint32_t dst, const CUtensorMap* map,
+                                          int row, int h, int b, uint32_t bar) {
+  mbar_arrive_expect_tx_lead(lead, bar, kTileBytes);
+  tma_load_4d_lead(lead, dst, map, 0, row, h, b, bar);
+  tma_load_4d_lead(lead, dst + kBoxBytes, map, 64, row, h, b, bar);
 }
 
 __device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CUtensorMap* tk,
                              const CUtensorMap* tv, uint32_t smem_q, uint32_t smem_kv,
-                             uint32_t bar0, WaitCtx& w) {
+                             uint32_t bar0, uint32_t lead, WaitCtx& w) {
+  // Run by the whole warp with uniform control flow; `lead` marks the one lane that issues.
   uint32_t stage = 0, empty_parity = 1;  // parity 1 passes on a fresh barrier
   uint32_t q_empty_parity = 1;
   // For the early-exit path: which "full" barriers were armed, and with which parity last.
@@ -337,11 +390,11 @@ __device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CU
 
   auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
   auto push_kv = [&](const CUtensorMap* map, int row, int h, int b, int site) -> bool {
-    if (!w.wait(bar(kBarKvEmpty + stage), empty_parity, site)) return false;
+    if (!w.wait_warp(bar(kBarKvEmpty + stage), empty_parity, site)) return false;
     const uint32_t full_parity = empty_parity ^ 1u;
     armed |= 1u << stage;
     armed_parity = (armed_parity & ~(1u << stage)) | (full_parity << stage);
-    load_tile(smem_kv + stage * kTileBytes, map, row, h, b, bar(kBarKvFull + stage));
+    load_tile(lead, smem_kv + stage * kTileBytes, map, row, h, b, bar(kBarKvFull + stage));
     if (++stage == kStages) {
       stage = 0;
       empty_parity ^= 1u;
@@ -353,11 +406,12 @@ __device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CU
     const ItemCoord c = decode_item(p, item);
     w.item = item;
     for (int q = 0; ok && q < kQTilesPerItem; ++q) {
-      ok = w.wait(bar(kBarQEmpty + q), q_empty_parity, 100 + q);
+      ok = w.wait_warp(bar(kBarQEmpty + q), q_empty_parity, 100 + q);
       if (!ok) break;
       armed |= 1u << (kStages + q);
       armed_parity = (armed_parity & ~(1u << (kStages + q))) | (q_full_parity << (kStages + q));
-      load_tile(smem_q + q * kTileBytes, tq, c.row0 + q * kBlockM, c.h, c.b, bar(kBarQFull + q));
+      load_tile(lead, smem_q + q * kTileBytes, tq, c.row0 + q * kBlockM, c.h, c.b,
+                bar(kBarQFull + q));
       if (q == 0) ok = push_kv(tk, 0, c.h, c.b, 110);  // K_0 right behind Q_0
     }
     q_empty_parity ^= 1u;
@@ -370,17 +424,15 @@ __device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CU
   }
 
   if (!ok || w.aborted()) {
-    // Leaving early: wait (bounded) for every copy this thread still has in flight, so no
-    // TMA write lands in shared memory after the CTA is gone.
-    WaitCtx quiet = w;
-    quiet.status = nullptr;
+    // Leaving early: wait (bounded) for every copy still in flight, so no TMA write lands in
+    // shared memory after the CTA is gone.
     for (int s = 0; s < kStages + kQTilesPerItem; ++s) {
       if (!((armed >> s) & 1u)) continue;
       const uint32_t b =
           (s < kStages) ? bar(kBarKvFull + s) : bar(kBarQFull + (s - kStages));
       const uint64_t t0 = global_timer_ns();
       while (!mbar_try_wait(b, (armed_parity >> s) & 1u, 1000)) {
-        if (global_timer_ns() - t0 > quiet.limit_ns) break;
+        if (global_timer_ns() - t0 > w.limit_ns) break;
       }
     }
   }
@@ -388,11 +440,13 @@ __device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CU
 
 // ---- MMA issuer ---------------------------------------------------------------------------
 __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_kv, uint32_t bar0,
-                            uint32_t tmem_base, WaitCtx& w) {
+                            uint32_t tmem_base, uint32_t lead, WaitCtx& w) {
+  // Run by the whole warp with uniform control flow; `lead` marks the one lane that issues.
   auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
   uint32_t stage = 0, full_parity = 0;
   uint32_t q_full_parity = 0;
-  uint32_t p_ready_parity[kQTilesPerItem] = {0, 0};
+  uint32_t p_parity = 0;       // kBarPReady / kBarPFull: both Q tiles see one phase per K/V tile
+  uint32_t o_free_parity = 1;  // passes on the fresh barrier: both accumulators start out free
   bool ok = true;
 
   auto advance = [&]() {
@@ -407,59 +461,75 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
     w.item = item;
     w.tile = 0;
     // ---- tile 0 scores for both Q tiles
-    if (!(ok = w.wait(bar(kBarKvFull + stage), full_parity, 200))) break;
+    if (!(ok = w.wait_warp(bar(kBarKvFull + stage), full_parity, 200))) break;
     {
       const uint32_t k_smem = smem_kv + stage * kTileBytes;
+#pragma unroll
       for (int q = 0; q < kQTilesPerItem; ++q) {
-        if (!(ok = w.wait(bar(kBarQFull + q), q_full_parity, 201 + q))) break;
+        if (!(ok = w.wait_warp(bar(kBarQFull + q), q_full_parity, 201 + q))) break;
         tc_fence_after_sync();
-        issue_qk(tmem_base + q * kBlockN, smem_q + q * kTileBytes, k_smem);
-        umma_commit(bar(kBarSFull + q));
-        if (T == 1) umma_commit(bar(kBarQEmpty + q));
+        issue_qk(lead, tmem_base + q * kBlockN, smem_q + q * kTileBytes, k_smem);
+        umma_commit_lead(lead, bar(kBarSFull + q));
+        if (T == 1) umma_commit_lead(lead, bar(kBarQEmpty + q));
       }
       if (!ok) break;
-      umma_commit(bar(kBarKvEmpty + stage));
+      umma_commit_lead(lead, bar(kBarKvEmpty + stage));
       advance();
     }
     q_full_parity ^= 1u;
 
     for (int i = 0; ok && i < T; ++i) {
       w.tile = i;
-      if (!(ok = w.wait(bar(kBarKvFull + stage), full_parity, 210))) break;
+      if (!(ok = w.wait_warp(bar(kBarKvFull + stage), full_parity, 210))) break;
       const uint32_t v_stage = stage;
       const uint32_t v_smem = smem_kv + v_stage * kTileBytes;
       advance();
       const bool has_next = (i + 1 < T);
+#pragma unroll
       for (int q = 0; q < kQTilesPerItem; ++q) {
         const uint32_t s_tmem = tmem_base + q * kBlockN;
         const uint32_t o_tmem = tmem_base + kQTilesPerItem * kBlockN + q * kHeadDim;
-        if (!(ok = w.wait(bar(kBarPReady + q), p_ready_parity[q], 220 + q))) break;
-        p_ready_parity[q] ^= 1u;
+        if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 0);
+        if (i == 0) {
+          // the previous item's epilogue must have read O_q out before it is overwritten
+          if (!(ok = w.wait_warp(bar(kBarOFree + q), o_free_parity, 240 + q))) break;
+        }
+        if (!(ok = w.wait_warp(bar(kBarPReady + q), p_parity, 220 + q))) break;
         tc_fence_after_sync();
-        issue_pv(o_tmem, s_tmem, v_smem, 0, kBlockN / 16, /*accumulate_first=*/i > 0);
-        if (q == kQTilesPerItem - 1) umma_commit(bar(kBarKvEmpty + v_stage));
+        if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 1);
+        issue_pv(lead, o_tmem, s_tmem, v_smem, 0, kPartAKSteps, /*accumulate_first=*/i > 0);
+        if (!(ok = w.wait_warp(bar(kBarPFull + q), p_parity, 225 + q))) break;
+        tc_fence_after_sync();
+        issue_pv(lead, o_tmem, s_tmem, v_smem, kPartAKSteps, kBlockN / 16, /*accumulate_first=*/true);
+        if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 2);
+        if (q == kQTilesPerItem - 1) umma_commit_lead(lead, bar(kBarKvEmpty + v_stage));
         if (!has_next) {
-          umma_commit(bar(kBarPvDone + q));
+          umma_commit_lead(lead, bar(kBarPvDone + q));
         } else {
           if (q == 0) {
-            if (!(ok = w.wait(bar(kBarKvFull + stage), full_parity, 230))) break;
+            if (!(ok = w.wait_warp(bar(kBarKvFull + stage), full_parity, 230))) break;
             tc_fence_after_sync();
           }
-          issue_qk(s_tmem, smem_q + q * kTileBytes, smem_kv + stage * kTileBytes);
-          umma_commit(bar(kBarSFull + q));
-          if (i + 2 == T) umma_commit(bar(kBarQEmpty + q));
+          if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 3);
+          issue_qk(lead, s_tmem, smem_q + q * kTileBytes, smem_kv + stage * kTileBytes);
+          if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 4);
+          umma_commit_lead(lead, bar(kBarSFull + q));
+          if (i + 2 == T) umma_commit_lead(lead, bar(kBarQEmpty + q));
           if (q == kQTilesPerItem - 1) {
-            umma_commit(bar(kBarKvEmpty + stage));
+            umma_commit_lead(lead, bar(kBarKvEmpty + stage));
             advance();
           }
         }
+        if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 5);
       }
+      p_parity ^= 1u;
     }
+    o_free_parity ^= 1u;
   }
 
   if (!ok || w.aborted()) {
-    // Leaving early: make sure nothing this thread issued is still running before TMEM goes.
-    umma_commit(bar(kBarDrain));
+    // Leaving early: make sure nothing this warp issued is still running before TMEM goes.
+    umma_commit_lead(lead, bar(kBarDrain));
     const uint64_t t0 = global_timer_ns();
     while (!mbar_try_wait(bar(kBarDrain), 0, 1000)) {
       if (global_timer_ns() - t0 > w.limit_ns) break;
@@ -467,38 +537,105 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
   }
 }
 
+// Which of the 16 column pairs of a 32-column chunk take the FMA-pipe polynomial instead of the
+// MUFU unit: B200ATTN_POLY_PER_16 / 2 of every 8 pairs, spread evenly so that MUFU and FMA work
+// alternate inside the instruction stream rather than coming in blocks.
+__device__ __forceinline__ constexpr bool use_poly(int j) {
+  constexpr int kPerEight = B200ATTN_POLY_PER_16 / 2;
+  const int k = j & 7;
+  return ((k + 1) * kPerEight) / 8 != (k * kPerEight) / 8;
+}
+
 // ---- softmax: one query row per thread ---------------------------------------------------
+// 2^(s * c - m) for one 32-column chunk: 16 packed bf16 pairs out, row-sum pairs accumulated.
+__device__ __forceinline__ void exp_chunk(const uint32_t (&s)[32], f2 scale2, f2 neg_m2,
+                                          uint32_t (&packed)[16], f2& sum_a, f2& sum_b) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const f2 x = f2_fma(f2_make(__uint_as_float(s[2 * j]), __uint_as_float(s[2 * j + 1])), scale2,
+                        neg_m2);
+    f2 e;
+    if (use_poly(j)) {
+      e = exp2_poly(x);
+    } else {
+      float x0, x1;
+      f2_split(x, x0, x1);
+      e = f2_make(ex2_approx(x0), ex2_approx(x1));
+    }
+    if (j & 1) sum_b = f2_add(sum_b, e); else sum_a = f2_add(sum_a, e);
+    float e0, e1;
+    f2_split(e, e0, e1);
+    packed[j] = pack_bf16x2(e0, e1);
+  }
+}
+
+__device__ __forceinline__ float row_max32(const uint32_t (&s)[32]) {
+  float m0 = kNegInf, m1 = kNegInf, m2 = kNegInf, m3 = kNegInf;
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    m0 = max3(m0, __uint_as_float(s[j + 0]), __uint_as_float(s[j + 1]));
+    m1 = max3(m1, __uint_as_float(s[j + 2]), __uint_as_float(s[j + 3]));
+    m2 = max3(m2, __uint_as_float(s[j + 4]), __uint_as_float(s[j + 5]));
+    m3 = max3(m3, __uint_as_float(s[j + 6]), __uint_as_float(s[j + 7]));
+  }
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+
+__device__ __forceinline__ float f2_hsum(f2 a, f2 b) {
+  float lo, hi;
+  f2_split(f2_add(a, b), lo, hi);
+  return lo + hi;
+}
+
+// Per K/V tile a thread turns its row of 128 scores into bf16 probabilities relative to the
+// row's reference maximum m and adds them to the running sum l.
+//
+// Tiles after the first do not start with a row-maximum pass. Part A (the first 96 columns) is
+// exponentiated speculatively against the current m; the speculation holds if its sum stays
+// below 2^kRebase (then no single probability reached 2^kRebase) and the exact maximum of part B
+// (32 columns, cheap) does not exceed m + kRebase. Otherwise, and always on the first tile, the
+// warp takes the exact path: reload the scores, take the true maximum, move m, multiply l and the
+// row's O accumulator in TMEM by 2^(m_old - m_new) (O is stable here: the scores of this tile
+// exist, so the previous PV has finished, and the next PV has not been released yet), and redo
+// part A. Nothing is published before the decision, so there is never anything to retract.
+// Part A is handed to the MMA warp first so its PV steps overlap the work on part B.
 __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, uint32_t tmem_base,
                                 int q, int warp_in_group, int lane, WaitCtx& w) {
   auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
+  constexpr float kRebase = B200ATTN_REBASE_LOG2;
+  const float sum_limit = exp2f(kRebase);
   const uint32_t lane_field = uint32_t(warp_in_group * 32) << 16;
   const uint32_t s_tmem = tmem_base + q * kBlockN + lane_field;
   const uint32_t p_tmem = s_tmem;  // bf16 P overwrites S columns 0..63
+  const uint32_t o_tmem = tmem_base + kQTilesPerItem * kBlockN + q * kHeadDim + lane_field;
   const int r = warp_in_group * 32 + lane;
   const float scale_log2 = p.scale_log2;
   const f2 scale2 = f2_splat(scale_log2);
   const int T = p.kv_tiles;
   const int tail_valid = p.len_kv - (T - 1) * kBlockN;  // keys in the last tile, 1..128
+  const bool tr = (warp_in_group == 0 && lane == 0);
   uint32_t s_parity = 0;
   uint32_t fin_free_parity = 1;  // passes on the fresh barrier: nothing to consume yet
 
   for (int item = blockIdx.x; item < p.total_items; item += gridDim.x) {
     w.item = item;
     w.tile = 0;
-    // The correction warps must have consumed the previous item's final (max, sum) before this
-    // group publishes anything for the next item. Besides protecting the two shared-memory
-    // slots it keeps this group at most one phase ahead on kBarStats and kBarFin even when an
-    // item has a single K/V tile. It costs nothing: the scores of the next item cannot exist
-    // before the previous item's last PV has finished, which is what the epilogue waits for.
+    // The epilogue warps must have consumed the previous item's final (max, sum) before this
+    // group publishes the next pair: it protects the two shared-memory slots and keeps kBarFin
+    // from completing twice before its waiters looked (parity waits would alias) when an item
+    // has a single K/V tile. It costs nothing: the scores of the next item cannot exist before
+    // the previous item's last PV has finished, which is what the epilogue waits for.
     if (!w.wait_warp(bar(kBarFinFree + q), fin_free_parity, 310 + q)) return;
     fin_free_parity ^= 1u;
     float m = kNegInf;  // reference maximum, log2 units
     float l = 0.0f;     // running sum of 2^(s - m)
     for (int i = 0; i < T; ++i) {
       w.tile = i;
+      if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 0);
       if (!w.wait_warp(bar(kBarSFull + q), s_parity, 300 + q)) return;
       s_parity ^= 1u;
       tc_fence_after_sync();
+      if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 1);
 
       uint32_t s[4][32];
       tmem_ld32(s_tmem + 0, s[0]);
@@ -506,61 +643,87 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
       tmem_ld32(s_tmem + 64, s[2]);
       tmem_ld32(s_tmem + 96, s[3]);
       tmem_wait_ld();
-      if (i == T - 1 && tail_valid < kBlockN) mask_tail(s, tail_valid);
+      if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 2);
+      const bool tail = (i == T - 1 && tail_valid < kBlockN);
+      if (tail) mask_tail(s, tail_valid);
 
-      const float tile_max = row_max(s) * scale_log2;
-      float rescale = 1.0f;
-      if (i == 0) {
-        m = tile_max;
-      } else {
-        const float m_new = fmaxf(m, tile_max);
-        if (m_new - m >= B200ATTN_RESCALE_THRESHOLD) {
-          rescale = ex2_approx(m - m_new);
-          l *= rescale;
-          m = m_new;
-        }
-      }
-      if (i > 0) {
-        // Tile 0 publishes nothing: there is no accumulator to rescale yet, and the correction
-        // warps do not wait for it (they may still be in the previous item's epilogue, so a
-        // tile-0 phase could complete twice before they looked, and parity would alias).
-        aux->rescale[q][r] = rescale;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(kBarStats + q));
-      }
-
-      const f2 neg_m2 = f2_splat(-m);
+      uint32_t packed[kPartAChunks][16];
       f2 sum_a = f2_splat(0.0f), sum_b = f2_splat(0.0f);
+      float sum_part_a = 0.0f;
+      bool exact = (i == 0);
+      if (!exact) {
+        const float max_b = row_max32(s[3]) * scale_log2;
+        const f2 neg_m2 = f2_splat(-m);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t packed[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const f2 x = f2_fma(f2_make(__uint_as_float(s[c][2 * j]), __uint_as_float(s[c][2 * j + 1])),
-                              scale2, neg_m2);
-          f2 e;
-          if ((j & 7) >= 8 - B200ATTN_POLY_PER_16 / 2) {
-            e = exp2_poly(x);
-          } else {
-            float x0, x1;
-            f2_split(x, x0, x1);
-            e = f2_make(ex2_approx(x0), ex2_approx(x1));
-          }
-          if (j & 1) sum_b = f2_add(sum_b, e); else sum_a = f2_add(sum_a, e);
-          float e0, e1;
-          f2_split(e, e0, e1);
-          packed[j] = pack_bf16x2(e0, e1);
-        }
-        tmem_st16(p_tmem + c * 16, packed);
+        for (int c = 0; c < kPartAChunks; ++c) exp_chunk(s[c], scale2, neg_m2, packed[c], sum_a, sum_b);
+        sum_part_a = f2_hsum(sum_a, sum_b);
+        // written so that a NaN sum also lands on the exact path
+        const bool bad = !(sum_part_a < sum_limit) || (max_b - m > kRebase);
+        exact = __any_sync(0xffffffffu, bad);
       }
+      if (tr) B200ATTN_TRACE_EVENT_AFTER(p, q, item, i, 0, 6, sum_part_a);
+      if (exact) {
+        if (i > 0) {
+          // part A's score registers were consumed by the speculation: fetch them again (S is
+          // still intact in TMEM, nothing has been stored over it yet)
+          tmem_ld32(s_tmem + 0, s[0]);
+          tmem_ld32(s_tmem + 32, s[1]);
+          tmem_ld32(s_tmem + 64, s[2]);
+          tmem_wait_ld();
+          if (tail) mask_tail(s, tail_valid);
+        }
+        const float tile_max = row_max(s) * scale_log2;
+        if (i == 0) {
+          m = tile_max;
+        } else {
+          const float m_new = fmaxf(m, tile_max);
+          const float f = ex2_approx(m - m_new);
+          m = m_new;
+          l *= f;
+          if (__any_sync(0xffffffffu, f != 1.0f)) {
+#pragma unroll 1
+            for (int c = 0; c < kHeadDim / 16; ++c) {
+              uint32_t acc[16];
+              tmem_ld16(o_tmem + c * 16, acc);
+              tmem_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) acc[j] = __float_as_uint(__uint_as_float(acc[j]) * f);
+              tmem_st16(o_tmem + c * 16, acc);
+            }
+            tmem_wait_st();
+          }
+        }
+        const f2 neg_m2 = f2_splat(-m);
+        sum_a = f2_splat(0.0f);
+        sum_b = f2_splat(0.0f);
+#pragma unroll
+        for (int c = 0; c < kPartAChunks; ++c) exp_chunk(s[c], scale2, neg_m2, packed[c], sum_a, sum_b);
+        sum_part_a = f2_hsum(sum_a, sum_b);
+      }
+      if (tr) B200ATTN_TRACE_EVENT_AFTER(p, q, item, i, 0, 3, sum_part_a);
+
+#pragma unroll
+      for (int c = 0; c < kPartAChunks; ++c) tmem_st16(p_tmem + c * 16, packed[c]);
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kBarPReady + q));
+      if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 4);
 
-      float a0, a1;
-      f2_split(f2_add(sum_a, sum_b), a0, a1);
-      l += a0 + a1;
+      // part B
+      {
+        const f2 neg_m2 = f2_splat(-m);
+        f2 sb_a = f2_splat(0.0f), sb_b = f2_splat(0.0f);
+        uint32_t packed_b[16];
+        exp_chunk(s[3], scale2, neg_m2, packed_b, sb_a, sb_b);
+        tmem_st16(p_tmem + kPartAChunks * 16, packed_b);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(kBarPFull + q));
+        l += sum_part_a + f2_hsum(sb_a, sb_b);
+      }
+      if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 5);
     }
     aux->row_max[q][r] = m;
     aux->row_sum[q][r] = l;
@@ -569,59 +732,19 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
   }
 }
 
-// ---- correction + epilogue -----------------------------------------------------------------
-__device__ void ws_correction_role(const FwdParams& p, WsAux* aux, uint32_t bar0,
-                                   uint32_t tmem_base, int warp_in_group, int lane, WaitCtx& w) {
+// ---- epilogue -------------------------------------------------------------------------------
+// Once per item and Q tile: take the final (max, sum) from the softmax group, read the
+// accumulator out of TMEM, normalise, optionally merge with a stored partial, store O / LSE.
+__device__ void ws_epilogue_role(const FwdParams& p, WsAux* aux, uint32_t bar0, uint32_t tmem_base,
+                                 int warp_in_group, int lane, WaitCtx& w) {
   auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
   const uint32_t lane_field = uint32_t(warp_in_group * 32) << 16;
   const int r = warp_in_group * 32 + lane;
-  const int T = p.kv_tiles;
-  uint32_t stats_parity[kQTilesPerItem] = {0, 0};
   uint32_t fin_parity = 0;
-
-  // Both O accumulators start out free: stand in for the "O safe" half of the first tile.
-  if (lane == 0) {
-    mbar_arrive(bar(kBarPReady + 0));
-    mbar_arrive(bar(kBarPReady + 1));
-  }
 
   for (int item = blockIdx.x; item < p.total_items; item += gridDim.x) {
     w.item = item;
-    // Tile 0 has nothing to rescale and its "O safe" vote was cast early (at kernel start, or
-    // by the previous item's epilogue), so the loop starts at tile 1.
-    for (int i = 1; i < T; ++i) {
-      w.tile = i;
-      for (int q = 0; q < kQTilesPerItem; ++q) {
-        if (!w.wait_warp(bar(kBarStats + q), stats_parity[q], 400 + q)) return;
-        stats_parity[q] ^= 1u;
-        const float f = aux->rescale[q][r];
-        if (__any_sync(0xffffffffu, f != 1.0f)) {
-          // The scores of tile i exist, so PV of tile i-1 (issued earlier by the same thread)
-          // has finished: O_q is stable.
-          tc_fence_after_sync();
-          const uint32_t o_tmem = tmem_base + kQTilesPerItem * kBlockN + q * kHeadDim + lane_field;
-#pragma unroll 1
-          for (int c = 0; c < kHeadDim / 32; ++c) {
-            uint32_t lo[16], hi[16];
-            tmem_ld16(o_tmem + c * 32, lo);
-            tmem_ld16(o_tmem + c * 32 + 16, hi);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              lo[j] = __float_as_uint(__uint_as_float(lo[j]) * f);
-              hi[j] = __float_as_uint(__uint_as_float(hi[j]) * f);
-            }
-            tmem_st16(o_tmem + c * 32, lo);
-            tmem_st16(o_tmem + c * 32 + 16, hi);
-          }
-          tmem_wait_st();
-          tc_fence_before_sync();
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(kBarPReady + q));
-      }
-    }
-
+    w.tile = p.kv_tiles;
     const ItemCoord c = decode_item(p, item);
     for (int q = 0; q < kQTilesPerItem; ++q) {
       if (!w.wait_warp(bar(kBarFin + q), fin_parity, 410 + q)) return;
@@ -637,7 +760,7 @@ __device__ void ws_correction_role(const FwdParams& p, WsAux* aux, uint32_t bar0
         // O_q is in registers: the next item's first PV may overwrite it.
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(kBarPReady + q));
+        if (lane == 0) mbar_arrive(bar(kBarOFree + q));
       });
     }
     fin_parity ^= 1u;
@@ -674,11 +797,12 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
         mbar_init(bar0 + 8u * (kBarQFull + q), 1);
         mbar_init(bar0 + 8u * (kBarQEmpty + q), 1);
         mbar_init(bar0 + 8u * (kBarSFull + q), 1);
-        mbar_init(bar0 + 8u * (kBarPReady + q), 8);
-        mbar_init(bar0 + 8u * (kBarStats + q), 4);
+        mbar_init(bar0 + 8u * (kBarPReady + q), 4);
+        mbar_init(bar0 + 8u * (kBarPFull + q), 4);
         mbar_init(bar0 + 8u * (kBarPvDone + q), 1);
         mbar_init(bar0 + 8u * (kBarFin + q), 4);
         mbar_init(bar0 + 8u * (kBarFinFree + q), 4);
+        mbar_init(bar0 + 8u * (kBarOFree + q), 4);
       }
       mbar_init(bar0 + 8u * kBarDrain, 1);
       mbar_init(bar0 + 8u * (kBarDrain + 1), 1);
@@ -704,19 +828,23 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
     reg_grow<kRegsSoftmax>();
     ws_softmax_role(p, aux, bar0, tmem_base, warp >> 2, warp & 3, lane, w);
   } else if (warp < 12) {
-    reg_shrink<kRegsCorrection>();
-    ws_correction_role(p, aux, bar0, tmem_base, warp & 3, lane, w);
+    reg_shrink<kRegsEpilogue>();
+    w.relaxed = true;
+    ws_epilogue_role(p, aux, bar0, tmem_base, warp & 3, lane, w);
   } else {
     reg_shrink<kRegsOther>();
+    const uint32_t lead = (lane == 0) ? 1u : 0u;
     if (warp == 12) {
-      if (lane == 0) ws_mma_role(p, smem_q, smem_kv, bar0, tmem_base, w);
+      ws_mma_role(p, smem_q, smem_kv, bar0, tmem_base, lead, w);
     } else if (warp == 13) {
-      if (lane == 0) {
+      if (lead) {
         tma_prefetch_desc(&tmap_q);
         tma_prefetch_desc(&tmap_k);
         tma_prefetch_desc(&tmap_v);
-        ws_load_role(p, &tmap_q, &tmap_k, &tmap_v, smem_q, smem_kv, bar0, w);
       }
+      __syncwarp();
+      w.relaxed = true;
+      ws_load_role(p, &tmap_q, &tmap_k, &tmap_v, smem_q, smem_kv, bar0, lead, w);
     }
     __syncwarp();
   }
@@ -802,19 +930,19 @@ attn_fwd_serial_kernel(const __grid_constant__ CUtensorMap tmap_q,
   float m = kNegInf, l = 0.0f;
   bool ok = true;
 
-  if (issuer) load_tile(smem_q, &tmap_q, row0, h, b, bar_q);
+  if (issuer) load_tile(1u, smem_q, &tmap_q, row0, h, b, bar_q);
 
   for (int i = 0; i < T; ++i) {
     w.tile = i;
     if (issuer) {
-      load_tile(smem_k, &tmap_k, i * kBlockN, h, b, bar_k);
-      load_tile(smem_v, &tmap_v, i * kBlockN, h, b, bar_v);
+      load_tile(1u, smem_k, &tmap_k, i * kBlockN, h, b, bar_k);
+      load_tile(1u, smem_v, &tmap_v, i * kBlockN, h, b, bar_v);
       armed_parity = kv_parity;
       ok = (i > 0) || w.wait(bar_q, 0, 500);
       ok = ok && w.wait(bar_k, kv_parity, 501);
       if (ok) {
         tc_fence_after_sync();
-        issue_qk(tmem_base, smem_q, smem_k);
+        issue_qk(1u, tmem_base, smem_q, smem_k);
       }
       umma_commit(bar_mma);  // always commit so nobody is left waiting for a missing arrival
     }
@@ -869,7 +997,7 @@ attn_fwd_serial_kernel(const __grid_constant__ CUtensorMap tmap_q,
       ok = w.wait(bar_v, kv_parity, 503);
       if (ok) {
         tc_fence_after_sync();
-        issue_pv(tmem_base + kBlockN, tmem_base, smem_v, 0, kBlockN / 16, i > 0);
+        issue_pv(1u, tmem_base + kBlockN, tmem_base, smem_v, 0, kBlockN / 16, i > 0);
       }
       umma_commit(bar_mma);
     }
@@ -914,7 +1042,7 @@ cudaError_t prepare_kernels() {
   cudaFuncAttributes fa;
   cudaError_t e = cudaFuncGetAttributes(&fa, attn_fwd_ws_kernel);
   if (e != cudaSuccess) return e;
-  constexpr int kPoolNeeded = 128 * (2 * kRegsSoftmax + kRegsCorrection + kRegsOther);
+  constexpr int kPoolNeeded = 128 * (2 * kRegsSoftmax + kRegsEpilogue + kRegsOther);
   if (fa.numRegs * kWsThreads < kPoolNeeded) return cudaErrorLaunchOutOfResources;
   e = cudaFuncSetAttribute(attn_fwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            kWsSmemBytes);

@@ -49,6 +49,7 @@ struct FwdParams {
   int32_t* status;      // kStatusInts ints the kernel can write (device or mapped host memory)
   uint32_t wait_limit_ms;
   PartialState partial;
+  long long* trace;  // clock64 samples for timeline studies; used only by B200ATTN_TRACE builds
 };
 
 // Launchers. Both return cudaGetLastError() of the launch.

@@ -209,6 +209,14 @@ int check_operand(const char* name, const b200attn_operand& t, int32_t batch, in
 }  // namespace host
 }  // namespace b200attn
 
+#ifdef B200ATTN_TRACE
+// Timeline studies only (never compiled into the shipped library): where block 0 records clock64.
+static long long* g_trace_buffer = nullptr;
+extern "C" B200ATTN_API void b200attn_debug_set_trace(void* device_buffer) {
+  g_trace_buffer = static_cast<long long*>(device_buffer);
+}
+#endif
+
 extern "C" {
 
 int b200attn_forward(const b200attn_forward_args* a) {
@@ -265,6 +273,9 @@ int b200attn_forward(const b200attn_forward_args* a) {
   p.partial.lse = a->partial_lse;
   p.partial.merge = a->partial_merge != 0;
   p.partial.emit = a->partial_emit != 0;
+#ifdef B200ATTN_TRACE
+  p.trace = g_trace_buffer;
+#endif
 
   CUtensorMap tq, tk, tv;
   const MapKey kq{a->q.ptr, a->q.stride_batch, a->q.stride_head, a->q.stride_row, a->batch, a->heads, a->len_q, device};

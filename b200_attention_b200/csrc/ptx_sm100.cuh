@@ -180,6 +180,79 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32
       : "memory");
 }
 
+// Warp-uniform issue: every lane of the warp executes these with identical operands and only the
+// lane with `lead != 0` issues the instruction. Keeping the surrounding control flow and the
+// operand arithmetic uniform lets the assembler keep descriptors in uniform registers instead of
+// funnelling them through per-thread registers for a single active lane.
+__device__ __forceinline__ void umma_ss_lead(uint32_t lead, uint32_t d_tmem, uint32_t a_lo,
+                                             uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p_acc, p_lead;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.u32 p_acc, %6, 0;\n\t"
+      "setp.ne.u32 p_lead, %7, 0;\n\t"
+      "@p_lead tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p_acc;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(lead)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_ts_lead(uint32_t lead, uint32_t d_tmem, uint32_t a_tmem,
+                                             uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p_acc, p_lead;\n\t"
+      ".reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.u32 p_acc, %5, 0;\n\t"
+      "setp.ne.u32 p_lead, %6, 0;\n\t"
+      "@p_lead tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p_acc;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(lead)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit_lead(uint32_t lead, uint32_t bar) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p_lead;\n\t"
+      "setp.ne.u32 p_lead, %1, 0;\n\t"
+      "@p_lead tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "}\n" ::"r"(bar),
+      "r"(lead)
+      : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx_lead(uint32_t lead, uint32_t bar,
+                                                           uint32_t bytes) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p_lead;\n\t"
+      "setp.ne.u32 p_lead, %2, 0;\n\t"
+      "@p_lead mbarrier.arrive.expect_tx.release.cta.shared::cta.b64 _, [%0], %1;\n\t"
+      "}\n" ::"r"(bar),
+      "r"(bytes), "r"(lead)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d_lead(uint32_t lead, uint32_t dst_smem, const void* tmap,
+                                                 int c0, int c1, int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p_lead;\n\t"
+      "setp.ne.u32 p_lead, %7, 0;\n\t"
+      "@p_lead cp.async.bulk.tensor.4d.shared::cta.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4, %5}], [%6];\n\t"
+      "}\n" ::"r"(dst_smem),
+      "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar), "r"(lead)
+      : "memory");
+}
+
 // The mbarrier receives one arrival once every MMA this thread issued so far has finished.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile(

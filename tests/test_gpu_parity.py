@@ -191,3 +191,22 @@ def test_many_back_to_back_launches_stay_clean(ops):
         torch.cuda.synchronize()
         _native.device_check()
         assert torch.equal(out, first)
+
+
+@pytest.mark.parametrize("kernel", [WS, SERIAL], ids=["ws", "serial"])
+def test_rebase_paths(ops, kernel):
+    # The production kernel speculates that a row's reference maximum still holds and falls back
+    # to an exact rebase (moving the maximum, rescaling l and O in TMEM) when a score exceeds it by
+    # more than 32 log2 units. Drive that path hard: (1) key norms that grow 40x along the
+    # sequence, (2) single outlier keys late in the sequence, placed in the first 96 columns of
+    # a tile (speculated part) and in the last 32 (checked part), far beyond any earlier score.
+    q, k, v = (O.to_bhld(t) for t in O.make_inputs_benchmark(1, 2, 256, 1024, seed=31))
+    ramp = torch.linspace(0.2, 8.0, 1024).view(1, 1, -1, 1)
+    run_and_check(ops, q, (k.float() * ramp).to(torch.bfloat16), v, kernel=kernel, scale=0.25)
+
+    q, k, v = (O.to_bhld(t) for t in O.make_inputs_benchmark(1, 2, 256, 1024, seed=32))
+    k = k.float()
+    k[:, :, 300] *= 30.0    # tile 2, column 44  -> part A
+    k[:, :, 750] *= 60.0    # tile 5, column 110 -> part B
+    k[:, :, 1023] *= 90.0   # last key of the last tile
+    run_and_check(ops, q, k.to(torch.bfloat16), v, kernel=kernel, scale=0.5)
