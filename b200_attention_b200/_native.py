@@ -113,7 +113,7 @@ def lib() -> C.CDLL:
         handle.b200attn_set_wait_limit_ms.restype = C.c_int
         handle.b200attn_launch_count.argtypes = []
         handle.b200attn_launch_count.restype = C.c_uint64
-        handle.b200attn_ipc_export.argtypes = [C.c_void_p, C.c_char_p]
+        handle.b200attn_ipc_export.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64)]
         handle.b200attn_ipc_export.restype = C.c_int
         handle.b200attn_ipc_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
         handle.b200attn_ipc_open.restype = C.c_int

@@ -321,7 +321,10 @@ __device__ __forceinline__ float row_max(const uint32_t (&s)[4][32]) {
 #endif
 // Number of leading 32-column chunks whose probabilities are published first ("part A"); the PV
 // MMAs over those keys start while the softmax warps still work on the rest ("part B").
-constexpr int kPartAChunks = 3;
+#ifndef B200ATTN_PART_A_CHUNKS
+#define B200ATTN_PART_A_CHUNKS 3
+#endif
+constexpr int kPartAChunks = B200ATTN_PART_A_CHUNKS;
 constexpr int kPartAKSteps = kPartAChunks * 2;  // K = 16 keys per MMA step
 
 constexpr int kStages = B200ATTN_KV_STAGES;

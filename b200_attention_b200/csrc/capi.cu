@@ -362,13 +362,32 @@ int b200attn_set_wait_limit_ms(uint32_t ms) {
 
 uint64_t b200attn_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
-int b200attn_ipc_export(const void* device_ptr, unsigned char handle[64]) {
+int b200attn_ipc_export(const void* device_ptr, unsigned char handle[64], uint64_t* offset_bytes) {
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
-  if (device_ptr == nullptr || handle == nullptr) return fail(B200ATTN_ERR_INVALID_ARGUMENT, "null argument");
+  if (device_ptr == nullptr || handle == nullptr || offset_bytes == nullptr)
+    return fail(B200ATTN_ERR_INVALID_ARGUMENT, "null argument");
+  // An IPC handle names a whole allocation: find its base and report where device_ptr sits in it.
+  using RangeFn = CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr);
+  static RangeFn range_fn = []() -> RangeFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    return reinterpret_cast<RangeFn>(p);
+  }();
+  if (range_fn == nullptr) return fail(B200ATTN_ERR_DRIVER, "cuMemGetAddressRange entry point not available");
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  const CUresult r = range_fn(&base, &size, reinterpret_cast<CUdeviceptr>(device_ptr));
+  if (r != CUDA_SUCCESS) return fail(B200ATTN_ERR_DRIVER, "cuMemGetAddressRange failed: not a device allocation?");
   cudaIpcMemHandle_t h;
-  const cudaError_t e = cudaIpcGetMemHandle(&h, const_cast<void*>(device_ptr));
+  const cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base));
   if (e != cudaSuccess) return fail_cuda("cudaIpcGetMemHandle", e);
   memcpy(handle, &h, 64);
+  *offset_bytes = uint64_t(reinterpret_cast<CUdeviceptr>(device_ptr) - base);
   return B200ATTN_OK;
 }
 

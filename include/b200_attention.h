@@ -109,9 +109,11 @@ B200ATTN_API int b200attn_set_wait_limit_ms(uint32_t ms);
 /* Number of kernels this library has launched in this process (all devices, all streams). */
 B200ATTN_API uint64_t b200attn_launch_count(void);
 
-/* Peer access for the sequence-parallel ring, one process per GPU:
- * export a handle for device memory owned by this process / map a peer's handle. */
-B200ATTN_API int b200attn_ipc_export(const void* device_ptr, unsigned char handle[64]);
+/* Peer access for the sequence-parallel ring, one process per GPU: export a handle for device
+ * memory owned by this process / map a peer's handle. A handle names a whole allocation;
+ * `offset_bytes` receives where device_ptr lies inside it (add it to the mapped base). */
+B200ATTN_API int b200attn_ipc_export(const void* device_ptr, unsigned char handle[64],
+                                     uint64_t* offset_bytes);
 B200ATTN_API int b200attn_ipc_open(const unsigned char handle[64], void** mapped_ptr);
 B200ATTN_API int b200attn_ipc_close(void* mapped_ptr);
 /* Copy `bytes` from a peer-mapped (or local) pointer into local memory on `stream`. */

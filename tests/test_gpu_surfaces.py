@@ -1,0 +1,137 @@
+"""GPU tests of the reference-shaped surfaces: the registry op (`module.sdpa`), the direct-BSHD
+op, the capstone op library and the attention callable, each against the CPU oracle, with the
+shapes / seeds / tolerances of the reference's own numerical tests where it has them
+(capstone-project/tests/test_kernel.py:78-143: H=32, seed 7, q,k x0.25; max-abs <= 0.15,
+rel-L2 < 5e-3, cosine > 0.9999, exactly one counted call)."""
+
+import pytest
+import torch
+
+from oracle import sdpa_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gpu(native_built):
+    if not torch.cuda.is_available():
+        pytest.fail("these tests need a CUDA device")
+    return native_built
+
+
+def test_registry_sdpa_matches_oracle(gpu):
+    from b200_attention_b200 import registry
+
+    module = registry.load_kernel(registry.resolve_kernel("b200"))
+    q, k, v = (O.to_bhld(t) for t in O.make_inputs_benchmark(2, 4, 512, 768, seed=0))
+    out = module.sdpa(q.cuda(), k.cuda(), v.cuda())
+    torch.cuda.synchronize()
+    module.device_check()
+    assert out.shape == q.shape and out.dtype == torch.bfloat16 and out.is_contiguous()
+    o_ref, lse_ref = O.sdpa_explicit(q, k, v)
+    O.assert_within_contract(O.compare(out.cpu(), o_ref))
+    o2, lse = module.sdpa_lse(q.cuda(), k.cuda(), v.cuda())
+    torch.cuda.synchronize()
+    O.assert_within_contract(O.compare(o2.cpu(), o_ref, lse.cpu(), lse_ref))
+    # the reference's own gate: rtol = atol = 3e-2 (benchmarks/check_correctness.py:27-28, 102)
+    torch.testing.assert_close(out.cpu().float(), o_ref, rtol=3e-2, atol=3e-2)
+
+
+def test_registry_bshd_needs_no_copies_and_matches_bhld(gpu):
+    from b200_attention_b200 import registry
+
+    bshd = registry.load_kernel(registry.resolve_kernel("b200_bshd"))
+    bhld = registry.load_kernel(registry.resolve_kernel("b200"))
+    q, k, v = (t.cuda() for t in O.make_inputs_benchmark(2, 4, 512, 512, seed=0))  # [B, L, H, 128]
+    out = bshd.sdpa(q, k, v)
+    ref = bhld.sdpa(*(t.transpose(1, 2).contiguous() for t in (q, k, v)))
+    torch.cuda.synchronize()
+    assert out.shape == q.shape
+    assert torch.equal(out.transpose(1, 2), ref)  # same kernel, same arithmetic, other strides
+    with pytest.raises(RuntimeError, match="contiguous"):
+        bshd.sdpa(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
+
+
+def test_registry_op_rejections(gpu):
+    from b200_attention_b200 import registry
+
+    module = registry.load_kernel(registry.resolve_kernel("b200"))
+    x = torch.zeros(1, 2, 256, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="bfloat16"):
+        module.sdpa(x.float(), x.float(), x.float())
+    with pytest.raises(RuntimeError, match="head_dim"):
+        module.sdpa(x[..., :64], x[..., :64], x[..., :64])
+    with pytest.raises(RuntimeError, match="4D"):
+        module.sdpa(x[0], x[0], x[0])
+    with pytest.raises(RuntimeError, match="same shape"):
+        module.sdpa(x, x, x[:, :, :128])
+
+
+def test_capstone_op_library(gpu):
+    torch.ops.load_library(str(gpu["ltx_op"]))
+    q, k, v = (O.to_bhld(t) for t in O.make_inputs_benchmark(1, 6, 512, 256, seed=3))
+    flat = lambda t: t.reshape(-1, t.shape[2], 128).cuda()
+    out = torch.ops.ltx_sm100.attention(flat(q), flat(k), flat(v))
+    torch.cuda.synchronize()
+    assert out.shape == (6, 512, 128)
+    o_ref, _ = O.sdpa_explicit(q, k, v)
+    O.assert_within_contract(O.compare(out.cpu().view(1, 6, 512, 128), o_ref))
+    with pytest.raises(RuntimeError, match="contiguous"):
+        torch.ops.ltx_sm100.attention(flat(q).transpose(0, 1), flat(k), flat(v))
+
+
+@pytest.mark.parametrize("lq,lk", [(1536, 1024), (1536, 1536), (3072, 1024)],
+                         ids=["cross", "self", "longer-cross"])
+def test_attention_callable_matches_fp32_sdpa(gpu, lq, lk):
+    from b200_attention_b200 import backend
+
+    heads = 32
+    q, k, v = O.make_inputs_capstone(heads, lq, lk, seed=7)
+    backend.reset_stats()
+    actual = backend.B200Attention()(q.cuda(), k.cuda(), v.cuda(), heads).float().cpu()
+    torch.cuda.synchronize()
+    split = lambda t: t.reshape(1, t.shape[1], heads, 128).transpose(1, 2)
+    reference = O.sdpa_torch_math(split(q), split(k), split(v)).transpose(1, 2).reshape_as(actual)
+    diff = actual - reference
+    assert torch.isfinite(actual).all()
+    assert float(diff.abs().max()) <= 0.15
+    assert float(diff.norm() / reference.norm().clamp_min(1e-12)) < 0.005
+    assert float(torch.nn.functional.cosine_similarity(actual.flatten(), reference.flatten(), dim=0)) > 0.9999
+    O.assert_within_contract(O.compare(actual, reference))
+    stats = backend.get_stats()
+    assert stats["total_calls"] == 1
+    assert list(stats["signatures"]) == [f"B=1,Lq={lq},Lkv={lk},H={heads},D=128,dtype=torch.bfloat16,device=cuda:0"]
+
+
+def test_attention_callable_rejects_mask_and_wrong_dtype(gpu):
+    from b200_attention_b200 import backend
+
+    attn = backend.B200Attention()
+    x = torch.zeros(1, 256, 256, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="unmasked"):
+        attn(x, x, x, 2, mask=torch.ones(1, device="cuda"))
+    with pytest.raises(RuntimeError, match="BF16"):
+        attn(x.float(), x.float(), x.float(), 2)
+    with pytest.raises(RuntimeError, match="head dimension 128"):
+        attn(x, x, x, 4)
+
+
+def test_shard_plan_execution_covers_everything(gpu):
+    # Two "ranks" run their (batch, head) plans one after the other on this GPU; together they
+    # must reproduce the unsharded result bit for bit (no collective involved).
+    from b200_attention_b200 import ops, sharding
+
+    for layout in ("bhld", "bshd"):
+        q, k, v = O.make_inputs_benchmark(3, 5, 256, 384, seed=5)
+        if layout == "bhld":
+            q, k, v = (O.to_bhld(t) for t in (q, k, v))
+        q, k, v = q.cuda(), k.cuda(), v.cuda()
+        whole, lse_whole = ops.attention(q, k, v, layout=layout, return_lse=True)
+        out = torch.zeros_like(q)
+        lse = torch.zeros_like(lse_whole)
+        for rank in range(4):
+            _, l = sharding.run_shard(q, k, v, sharding.plan(3, 5, 4, rank), layout=layout, out=out,
+                                      return_lse=True)
+            lse += l
+        torch.cuda.synchronize()
+        assert torch.equal(out, whole) and torch.equal(lse, lse_whole)

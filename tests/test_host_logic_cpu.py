@@ -1,0 +1,183 @@
+"""CPU tests of the host-side logic: registry and backend contracts (mirroring the reference's
+own contract tests, capstone-project/tests/test_kernel.py:33-75, 146-177 and
+tests/test_ltx_routing.py:147-190), (batch, head) sharding plans, the ring schedule, and a
+world_size-2 gloo run of both multi-GPU plans with the arithmetic done by the CPU oracle."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from b200_attention_b200 import backend, registry, ring, sharding
+from oracle import sdpa_oracle as O
+
+
+# ---------------------------------------------------------------------------------- registry
+def test_registry_resolves_kernels_and_shapes():
+    spec = registry.resolve_kernel("b200")
+    assert spec.launch_symbol == "b200attn_bhld_launch" and spec.len_q_multiple == 1
+    assert registry.resolve_kernel(20).layout == "bshd"
+    assert registry.resolve_kernel("b200attn_bshd_launch").op_name == "sdpa_bshd"
+    with pytest.raises(ValueError):
+        registry.resolve_kernel("")
+    with pytest.raises(ValueError):
+        registry.resolve_kernel("18")
+    assert registry.resolve_shape("paper8k") == ("paper8k", 4, 16, 8192, 8192)
+    with pytest.raises(ValueError):
+        registry.resolve_shape("paper1k")
+    assert len(registry.source_closure_sha256(spec)) == 64
+
+
+def test_registry_loads_shim_and_refuses_cpu_tensors(native_built):
+    module = registry.load_kernel(registry.resolve_kernel("b200"))
+    x = torch.zeros(1, 2, 256, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="must be CUDA tensors"):
+        module.sdpa(x, x, x)
+
+
+# ----------------------------------------------------------------------------------- backend
+def test_backend_constructor_is_lazy_and_mask_is_rejected_first():
+    attn = backend.B200Attention()
+    assert attn.label == "B200Attention" and attn._loaded is False
+    # a mask is refused before any tensor or CUDA check: arbitrary objects are fine here
+    with pytest.raises(RuntimeError, match="unmasked"):
+        attn(object(), object(), object(), 32, mask=object())
+
+
+def test_backend_rejections():
+    attn = backend.B200Attention()
+    x = torch.zeros(1, 256, 256, dtype=torch.bfloat16)
+    with pytest.raises(TypeError):
+        attn(x, x, "v", 2)
+    for bad_heads in (0, -1, 2.0, True):
+        with pytest.raises(ValueError):
+            attn(x, x, x, bad_heads)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        attn(x, x, x, 2)
+    backend.reset_stats()
+    assert backend.get_stats() == {"total_calls": 0, "signatures": {}, "unique_inputs": []}
+
+
+def test_backend_hook_receives_the_exact_callable():
+    # `with_attention` of the video model returns a new stage holding the callable it was given
+    class FakeStage:
+        def __init__(self, attention=None):
+            self.attention = attention
+
+        def with_attention(self, fn):
+            return FakeStage(fn)
+
+    attn = backend.B200Attention()
+    base = FakeStage()
+    routed = base.with_attention(attn)
+    assert routed is not base and routed.attention is attn and base.attention is None
+
+
+def test_stats_signature_format():
+    q = torch.zeros(1, 512, 256, dtype=torch.bfloat16)
+    k = torch.zeros(1, 128, 256, dtype=torch.bfloat16)
+    backend.reset_stats()
+    backend._record_success(q, k, k, batch=1, query_length=512, key_value_length=128, heads=2, head_dim=128)
+    backend._record_success(q, k, k, batch=1, query_length=512, key_value_length=128, heads=2, head_dim=128)
+    stats = backend.get_stats()
+    assert stats["total_calls"] == 2
+    assert stats["signatures"] == {"B=1,Lq=512,Lkv=128,H=2,D=128,dtype=torch.bfloat16,device=cpu": 2}
+    assert len(stats["unique_inputs"]) == 1
+    backend.reset_stats()
+
+
+# ---------------------------------------------------------------------------------- sharding
+@pytest.mark.parametrize("batch,heads,world", [(4, 16, 1), (4, 16, 2), (4, 16, 8), (1, 12, 8), (3, 5, 4), (1, 1, 4)])
+def test_sharding_plan_partitions_every_unit_once(batch, heads, world):
+    seen = []
+    for r in range(world):
+        for hr in sharding.plan(batch, heads, world, r):
+            assert 0 <= hr.head_begin < hr.head_end <= heads and 0 <= hr.batch < batch
+            seen += [(hr.batch, h) for h in range(hr.head_begin, hr.head_end)]
+    assert sorted(seen) == [(b, h) for b in range(batch) for h in range(heads)]
+    counts = [sharding.units_of(p) for p in sharding.plan_all(batch, heads, world)]
+    assert max(counts) - min(counts) <= 1
+
+
+def test_sharding_main_config_is_even():
+    for world in (1, 2, 4, 8):
+        assert sharding.imbalance(4, 16, world) == 1.0
+    assert sharding.flat_bounds(64, 8, 3) == (24, 32)
+    with pytest.raises(ValueError):
+        sharding.flat_bounds(8, 2, 2)
+
+
+# -------------------------------------------------------------------------------------- ring
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_ring_schedule_and_flags(world):
+    for r in range(world):
+        order = ring.ring_schedule(world, r)
+        assert order[0] == r and sorted(order) == list(range(world))
+    # at every step each shard is read by exactly one rank
+    for s in range(world):
+        assert sorted(ring.ring_schedule(world, r)[s] for r in range(world)) == list(range(world))
+    flags = ring.chain_flags(world)
+    assert flags[0][0] is False and flags[-1][1] is False
+    assert all(m for m, _ in flags[1:]) and all(e for _, e in flags[:-1])
+    for step in ring.pull_plan(world):
+        assert sorted(o for _, o in step) == list(range(world))
+        assert all(reader != owner for reader, owner in step)
+
+
+# ------------------------------------------------------------------------ gloo, world size 2
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, result_queue):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        B, H, L = 2, 3, 64
+        q, k, v = (O.to_bhld(t) for t in O.make_inputs_benchmark(B, H, L, L, seed=40))
+        full_o, full_lse = O.sdpa_explicit(q, k, v)
+
+        # (batch, head) sharding: each rank computes its slices; all_reduce only assembles them
+        out = torch.zeros_like(full_o)
+        for hr in sharding.plan(B, H, world, rank):
+            sl = (slice(hr.batch, hr.batch + 1), slice(hr.head_begin, hr.head_end))
+            out[sl], _ = O.sdpa_explicit(q[sl], k[sl], v[sl])
+        dist.all_reduce(out)
+        ok_shard = bool((out - full_o).abs().max() < 1e-5)
+
+        # sequence-parallel ring: rows of Q sharded, K/V shards visited in ring order and merged
+        rows = slice(rank * L // world, (rank + 1) * L // world)
+        shards = [(k[:, :, r * L // world:(r + 1) * L // world], v[:, :, r * L // world:(r + 1) * L // world])
+                  for r in range(world)]
+        acc = None
+        for step, (merge, emit) in zip(ring.ring_schedule(world, rank), ring.chain_flags(world)):
+            o_s, lse_s = O.sdpa_explicit(q[:, :, rows], *shards[step])
+            acc = (o_s, lse_s) if not merge else O.merge_partials(acc[0], acc[1], o_s, lse_s)
+        ok_ring = bool((acc[0] - full_o[:, :, rows]).abs().max() < 1e-5 and
+                       (acc[1] - full_lse[:, :, rows]).abs().max() < 1e-5)
+        flags = torch.tensor([int(ok_shard), int(ok_ring)])
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        if rank == 0:
+            result_queue.put(flags.tolist())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_gloo_sharding_and_ring():
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, queue)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert queue.get(timeout=10) == [1, 1]
