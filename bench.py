@@ -56,6 +56,11 @@ WORKLOADS = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu summary of the
+# workload (profiles/attn_fwd_ws_kernel_main_B4_H16_L8192.md); None where nothing was captured.
+NCU_TRAFFIC_BYTES = {"main": 516.2e6}
+
+
 def flops(b, h, lq, lk):
     return 4.0 * b * h * lq * lk * HEAD_DIM
 
@@ -90,7 +95,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-i", str(self.index), "-lms", "100"],
+                 "-i", str(self.index), "-lms", "25"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -325,13 +330,7 @@ def run_ours(args, rank, local_rank, world):
 
     if rank == 0:
         peaks = measured_peaks()
-        traffic = None
-        tpath = ROOT / "profiles" / "traffic.json"
-        if tpath.exists():
-            try:
-                traffic = json.loads(tpath.read_text()).get(args.workload)
-            except Exception:
-                traffic = None
+        traffic = NCU_TRAFFIC_BYTES.get(args.workload)
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
