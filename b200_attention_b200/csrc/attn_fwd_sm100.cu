@@ -54,6 +54,9 @@ constexpr uint32_t kIdescPV = umma_idesc_bf16(kBlockM, kHeadDim, /*b_mn_major=*/
 // fixed points of its first work item, for tiles [kTraceTile0, kTraceTile0 + kTraceTiles).
 // Layout: trace[((role * kTraceTiles + tile) * 2 + q) * 8 + event].
 #ifdef B200ATTN_TRACE
+#ifndef B200ATTN_TRACE_WARP
+#define B200ATTN_TRACE_WARP 0
+#endif
 constexpr int kTraceTile0 = 8, kTraceTiles = 16;
 #define B200ATTN_TRACE_EVENT(p, role, item, tile, q, ev)                                          \
   do {                                                                                            \
@@ -616,7 +619,11 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
   const f2 scale2 = f2_splat(scale_log2);
   const int T = p.kv_tiles;
   const int tail_valid = p.len_kv - (T - 1) * kBlockN;  // keys in the last tile, 1..128
-  const bool tr = (warp_in_group == 0 && lane == 0);
+#ifdef B200ATTN_TRACE
+  const bool tr = (warp_in_group == B200ATTN_TRACE_WARP && lane == 0);
+#else
+  const bool tr = false;
+#endif
   uint32_t s_parity = 0;
   uint32_t fin_free_parity = 1;  // passes on the fresh barrier: nothing to consume yet
 
@@ -658,14 +665,20 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
         const float max_b = row_max32(s[3]) * scale_log2;
         const f2 neg_m2 = f2_splat(-m);
 #pragma unroll
-        for (int c = 0; c < kPartAChunks; ++c) exp_chunk(s[c], scale2, neg_m2, packed[c], sum_a, sum_b);
+        for (int c = 0; c < kPartAChunks; ++c) {
+          exp_chunk(s[c], scale2, neg_m2, packed[c], sum_a, sum_b);
+#ifdef B200ATTN_TRACE_FINE
+          if (tr && c == 0) B200ATTN_TRACE_EVENT_AFTER(p, q, item, i, 0, 7, __uint_as_float(packed[0][15]));
+          if (tr && c == 1) B200ATTN_TRACE_EVENT_AFTER(p, q, item, i, 0, 0, __uint_as_float(packed[1][15]));
+#endif
+        }
         sum_part_a = f2_hsum(sum_a, sum_b);
         // written so that a NaN sum also lands on the exact path
         const bool bad = !(sum_part_a < sum_limit) || (max_b - m > kRebase);
         exact = __any_sync(0xffffffffu, bad);
       }
       if (tr) B200ATTN_TRACE_EVENT_AFTER(p, q, item, i, 0, 6, sum_part_a);
-      if (exact) {
+      if (__builtin_expect(exact, 0)) {
         if (i > 0) {
           // part A's score registers were consumed by the speculation: fetch them again (S is
           // still intact in TMEM, nothing has been stored over it yet)
