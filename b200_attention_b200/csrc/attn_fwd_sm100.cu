@@ -132,6 +132,13 @@ struct WaitCtx {
     return wait_slow(bar, parity, site);
   }
 
+  // For the two issue warps (MMA, TMA): every lane polls for itself and nothing warp-collective
+  // follows, so no vote is needed; lanes re-join at the next __syncwarp.
+  __device__ __forceinline__ bool wait_lanes(uint32_t bar, uint32_t parity, int site) const {
+    if (mbar_try_wait(bar, parity, 0)) return true;
+    return wait_slow(bar, parity, site);
+  }
+
   // For roles run by whole warps: every lane returns the same answer, so the warp stays
   // converged for the .sync.aligned TMEM instructions that follow.
   __device__ __forceinline__ bool wait_warp(uint32_t bar, uint32_t parity, int site) const {
@@ -322,10 +329,13 @@ __device__ __forceinline__ float row_max(const uint32_t (&s)[4][32]) {
 #ifndef B200ATTN_REBASE_LOG2
 #define B200ATTN_REBASE_LOG2 32.0f
 #endif
-// Number of leading 32-column chunks whose probabilities are published first ("part A"); the PV
-// MMAs over those keys start while the softmax warps still work on the rest ("part B").
+// Number of leading 32-column chunks whose probabilities are published first ("part A"); with
+// fewer than 4 the PV MMAs over those keys start while the softmax warps still work on the rest
+// ("part B", whose exact maximum is then checked up front). Measured at B4 H16 L8192: 4 (no
+// split, no maximum at all) 1254 TFLOPS, 3 -> 1243, 2 -> 1212: the sub-partitions' issue slots,
+// not the P -> PV latency, are what is scarce, so the variant with the fewest instructions wins.
 #ifndef B200ATTN_PART_A_CHUNKS
-#define B200ATTN_PART_A_CHUNKS 3
+#define B200ATTN_PART_A_CHUNKS 4
 #endif
 constexpr int kPartAChunks = B200ATTN_PART_A_CHUNKS;
 constexpr int kPartAKSteps = kPartAChunks * 2;  // K = 16 keys per MMA step
@@ -495,6 +505,11 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
       for (int q = 0; q < kQTilesPerItem; ++q) {
         const uint32_t s_tmem = tmem_base + q * kBlockN;
         const uint32_t o_tmem = tmem_base + kQTilesPerItem * kBlockN + q * kHeadDim;
+        if (q == 0 && has_next) {
+          // the next K tile landed long ago; checking it here keeps the check off the
+          // P -> PV -> QK -> S chain
+          if (!(ok = w.wait_warp(bar(kBarKvFull + stage), full_parity, 230))) break;
+        }
         if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 0);
         if (i == 0) {
           // the previous item's epilogue must have read O_q out before it is overwritten
@@ -504,18 +519,16 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
         tc_fence_after_sync();
         if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 1);
         issue_pv(lead, o_tmem, s_tmem, v_smem, 0, kPartAKSteps, /*accumulate_first=*/i > 0);
-        if (!(ok = w.wait_warp(bar(kBarPFull + q), p_parity, 225 + q))) break;
-        tc_fence_after_sync();
-        issue_pv(lead, o_tmem, s_tmem, v_smem, kPartAKSteps, kBlockN / 16, /*accumulate_first=*/true);
+        if (kPartAChunks < 4) {
+          if (!(ok = w.wait_warp(bar(kBarPFull + q), p_parity, 225 + q))) break;
+          tc_fence_after_sync();
+          issue_pv(lead, o_tmem, s_tmem, v_smem, kPartAKSteps, kBlockN / 16, /*accumulate_first=*/true);
+        }
         if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 2);
         if (q == kQTilesPerItem - 1) umma_commit_lead(lead, bar(kBarKvEmpty + v_stage));
         if (!has_next) {
           umma_commit_lead(lead, bar(kBarPvDone + q));
         } else {
-          if (q == 0) {
-            if (!(ok = w.wait_warp(bar(kBarKvFull + stage), full_parity, 230))) break;
-            tc_fence_after_sync();
-          }
           if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 3);
           issue_qk(lead, s_tmem, smem_q + q * kTileBytes, smem_kv + stage * kTileBytes);
           if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 4);
@@ -662,7 +675,10 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
       float sum_part_a = 0.0f;
       bool exact = (i == 0);
       if (!exact) {
-        const float max_b = row_max32(s[3]) * scale_log2;
+        float max_b = kNegInf;
+#pragma unroll
+        for (int c = kPartAChunks; c < 4; ++c) max_b = fmaxf(max_b, row_max32(s[c]));
+        max_b *= scale_log2;
         const f2 neg_m2 = f2_splat(-m);
 #pragma unroll
         for (int c = 0; c < kPartAChunks; ++c) {
@@ -682,9 +698,8 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
         if (i > 0) {
           // part A's score registers were consumed by the speculation: fetch them again (S is
           // still intact in TMEM, nothing has been stored over it yet)
-          tmem_ld32(s_tmem + 0, s[0]);
-          tmem_ld32(s_tmem + 32, s[1]);
-          tmem_ld32(s_tmem + 64, s[2]);
+#pragma unroll
+          for (int c = 0; c < kPartAChunks; ++c) tmem_ld32(s_tmem + c * 32, s[c]);
           tmem_wait_ld();
           if (tail) mask_tail(s, tail_valid);
         }
@@ -730,13 +745,18 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
       {
         const f2 neg_m2 = f2_splat(-m);
         f2 sb_a = f2_splat(0.0f), sb_b = f2_splat(0.0f);
-        uint32_t packed_b[16];
-        exp_chunk(s[3], scale2, neg_m2, packed_b, sb_a, sb_b);
-        tmem_st16(p_tmem + kPartAChunks * 16, packed_b);
-        tmem_wait_st();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(kBarPFull + q));
+#pragma unroll
+        for (int c = kPartAChunks; c < 4; ++c) {
+          uint32_t packed_b[16];
+          exp_chunk(s[c], scale2, neg_m2, packed_b, sb_a, sb_b);
+          tmem_st16(p_tmem + c * 16, packed_b);
+        }
+        if (kPartAChunks < 4) {
+          tmem_wait_st();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(kBarPFull + q));
+        }
         l += sum_part_a + f2_hsum(sb_a, sb_b);
       }
       if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 5);

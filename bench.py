@@ -54,6 +54,12 @@ WORKLOADS = {
     "dit_cross": (1, 12, 32768, 512, "bshd"),
     "smoke": (1, 4, 1024, 1024, "bhld"),
 }
+# Sequence-parallel long-context workload: the GLOBAL problem (batch, heads, len) is fixed and
+# split by query rows / key rows over the ranks (strong scaling; needs --gpus >= 2 to be a ring).
+RING_WORKLOADS = {
+    "sp_ring": (1, 32, 131072),
+    "sp_ring_small": (1, 8, 16384),
+}
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu summary of the
@@ -356,6 +362,94 @@ def run_ours(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+def run_ring(args, rank, local_rank, world):
+    """K/V ring over `world` GPUs: Q rows and K/V rows sharded, shards pulled over NVLink P2P,
+    partial (O, LSE) merged in the kernel epilogue. value = global FLOPs / max-over-ranks time."""
+    import torch
+    import torch.distributed as dist
+
+    from b200_attention_b200 import _native
+    from b200_attention_b200.ring import RingAttention
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    os.environ.setdefault("MASTER_PORT", "29533")
+    dist.init_process_group("nccl", device_id=dev, rank=rank, world_size=world)
+    B, H, L = RING_WORKLOADS[args.workload]
+    n = L // world
+    g = torch.Generator().manual_seed(4321 + rank)
+    host = [torch.randn(B, H, n, HEAD_DIM, generator=g).to(torch.bfloat16).pin_memory() for _ in range(3)]
+    q, k, v = (t.to(dev) for t in host)
+    o_host = torch.empty(B, H, n, HEAD_DIM, dtype=torch.bfloat16).pin_memory()
+    ra = RingAttention()
+    stream = torch.cuda.current_stream(dev)
+
+    def max_over_ranks(x):
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for _ in range(max(args.warmup, 3)):
+        ra.forward(q, k, v)
+    launches0 = _native.launch_count()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    if rank == 0:
+        sampler.start()
+    torch.cuda.synchronize(dev)
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        ra.forward(q, k, v)
+    e1.record(stream)
+    torch.cuda.synchronize(dev)
+    dist.barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    launches = _native.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    # end to end: shards from pinned host memory in, O back out, every step
+    e2e_steps = max(2, min(args.steps, 3))
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        for d, h in zip((q, k, v), host):
+            d.copy_(h, non_blocking=True)
+        o, _ = ra.forward(q, k, v)
+        o_host.copy_(o, non_blocking=True)
+    e1.record(stream)
+    torch.cuda.synchronize(dev)
+    dist.barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
+    ra.unbind()
+    total = flops(B, H, L, L)
+    if rank == 0:
+        peaks = measured_peaks()
+        value = total / (ms * 1e-3) / 1e12
+        shard_bytes = 2 * B * H * n * HEAD_DIM * 2
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: sequence-parallel K/V ring, global B={B} H={H} "
+                                   f"Lq=Lk={L} D=128 bf16 N(0,1), Q and K/V rows sharded x{world}",
+                       "global_batch": B, "heads": H, "len_q": L, "len_kv": L, "head_dim": HEAD_DIM,
+                       "parallelism": f"sequence-parallel ring x{world}: NVLink P2P pulls into a local "
+                                      "double buffer, (O, LSE) merged in the kernel epilogue, no collective",
+                       "l2_policy": "per-step operands exceed the 126 MB L2; no flush"},
+            "pct_of_bf16_peak": 100.0 * value / world / peaks["bf16_tflops"],
+            "roofline": {"bound": "tensor", "achieved": value / world, "peak": peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": value / world / peaks["bf16_tflops"],
+                         "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "traffic": None,
+                         "nvlink_bytes_per_gpu_per_step": shard_bytes * (world - 1),
+                         "nvlink_gbs_needed": shard_bytes * (world - 1) / (ms * 1e-3) / 1e9},
+            "e2e": {"value": total / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS",
+                    "h2d_bytes_per_step": 3 * host[0].numel() * 2 * world,
+                    "d2h_bytes_per_step": o_host.numel() * 2 * world, "ms_per_step": e2e_ms},
+            "gpu_launches": int(launches), "clocks": clocks, "cpu_baseline": None, "k18_same_gpu": None,
+        }
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
 def time_k18(torch, q, k, v, layout, args):
     try:
         from oracle import native_refs as R
@@ -392,7 +486,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="main", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="main", choices=sorted(WORKLOADS) + sorted(RING_WORKLOADS))
     ap.add_argument("--no-k18", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=12.0)
@@ -402,6 +496,14 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if args.workload in RING_WORKLOADS:
+        if args.impl == "reference":
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable":
+                                  "the reference project has no sequence-parallel path; use --workload main"}))
+            return
+        run_ring(args, rank, local_rank, world)
+        return
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
         return
