@@ -132,11 +132,13 @@ struct WaitCtx {
     return wait_slow(bar, parity, site);
   }
 
-  // For the two issue warps (MMA, TMA): every lane polls for itself and nothing warp-collective
-  // follows, so no vote is needed; lanes re-join at the next __syncwarp.
-  __device__ __forceinline__ bool wait_lanes(uint32_t bar, uint32_t parity, int site) const {
-    if (mbar_try_wait(bar, parity, 0)) return true;
-    return wait_slow(bar, parity, site);
+  // For the MMA and TMA roles: whole-warp (voted) or single-lane execution, chosen at compile time.
+  __device__ __forceinline__ bool wait_issue(uint32_t bar, uint32_t parity, int site) const {
+#ifdef B200ATTN_ISSUE_SINGLE_LANE
+    return wait(bar, parity, site);
+#else
+    return wait_warp(bar, parity, site);
+#endif
   }
 
   // For roles run by whole warps: every lane returns the same answer, so the warp stays
@@ -152,19 +154,23 @@ struct WaitCtx {
 // ------------------------------------------------------------------------------------------
 // MMA issue helpers (called by one thread)
 // ------------------------------------------------------------------------------------------
-// S[128 x 128] = Q_tile * K_tile^T, eight K=16 steps over head_dim. Executed by a whole warp with
-// uniform operands; only the lane with lead != 0 issues.
+// S[128 x 128] = Q_tile * K_tile^T, eight K=16 steps over head_dim. Called by a whole warp with
+// uniform operands (so descriptors live in uniform registers); the lane with lead != 0 issues the
+// eight MMAs inside one branch. Measured at B4 H16 L8192: whole-warp roles 1311 TFLOPS, the
+// same roles run by a single lane 1080.
 __device__ __forceinline__ void issue_qk(uint32_t lead, uint32_t s_tmem, uint32_t q_smem,
                                          uint32_t k_smem) {
   constexpr uint32_t hi = umma_desc_hi_sw128(kSwizzleGroupBytes);
   const uint32_t a0 = umma_desc_lo(q_smem, 0);
   const uint32_t b0 = umma_desc_lo(k_smem, 0);
+  if (lead) {
 #pragma unroll
-  for (int kk = 0; kk < kHeadDim / 16; ++kk) {
-    // the address field counts 16-byte units
-    const uint32_t off = uint32_t(((kk >> 2) * kBoxBytes + (kk & 3) * 32) >> 4);
-    umma_ss_lead(lead, s_tmem, a0 + off, hi, b0 + off, hi, kIdescQK, kk > 0 ? 1u : 0u);
+    for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+      const uint32_t off = uint32_t(((kk >> 2) * kBoxBytes + (kk & 3) * 32) >> 4);
+      umma_ss(s_tmem, a0 + off, hi, b0 + off, hi, kIdescQK, kk > 0 ? 1u : 0u);
+    }
   }
+  __syncwarp();
 }
 
 // O[128 x 128] (+)= P[128 x 128 keys] * V_tile, K steps [kk_begin, kk_end). P is bf16 pairs in
@@ -174,13 +180,16 @@ __device__ __forceinline__ void issue_pv(uint32_t lead, uint32_t o_tmem, uint32_
                                          bool accumulate_first) {
   constexpr uint32_t hi = umma_desc_hi_sw128(kSwizzleGroupBytes);
   const uint32_t b0 = umma_desc_lo(v_smem, kBoxBytes);
+  if (lead) {
 #pragma unroll
-  for (int kk = 0; kk < kBlockN / 16; ++kk) {
-    if (kk < kk_begin || kk >= kk_end) continue;
-    const uint32_t off = uint32_t((kk * 16 * 128) >> 4);
-    const uint32_t acc = (kk > kk_begin || accumulate_first) ? 1u : 0u;
-    umma_ts_lead(lead, o_tmem, p_tmem + kk * 8, b0 + off, hi, kIdescPV, acc);
+    for (int kk = 0; kk < kBlockN / 16; ++kk) {
+      if (kk < kk_begin || kk >= kk_end) continue;
+      const uint32_t off = uint32_t((kk * 16 * 128) >> 4);
+      const uint32_t acc = (kk > kk_begin || accumulate_first) ? 1u : 0u;
+      umma_ts(o_tmem, p_tmem + kk * 8, b0 + off, hi, kIdescPV, acc);
+    }
   }
+  __syncwarp();
 }
 
 // ------------------------------------------------------------------------------------------
@@ -340,6 +349,9 @@ __device__ __forceinline__ float row_max(const uint32_t (&s)[4][32]) {
 constexpr int kPartAChunks = B200ATTN_PART_A_CHUNKS;
 constexpr int kPartAKSteps = kPartAChunks * 2;  // K = 16 keys per MMA step
 
+#ifndef B200ATTN_S_WAIT_SLEEP_NS
+#define B200ATTN_S_WAIT_SLEEP_NS 0
+#endif
 constexpr int kStages = B200ATTN_KV_STAGES;
 constexpr int kWsThreads = 512;
 constexpr int kRegsSoftmax = 192;
@@ -406,7 +418,7 @@ __device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CU
 
   auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
   auto push_kv = [&](const CUtensorMap* map, int row, int h, int b, int site) -> bool {
-    if (!w.wait_warp(bar(kBarKvEmpty + stage), empty_parity, site)) return false;
+    if (!w.wait_issue(bar(kBarKvEmpty + stage), empty_parity, site)) return false;
     const uint32_t full_parity = empty_parity ^ 1u;
     armed |= 1u << stage;
     armed_parity = (armed_parity & ~(1u << stage)) | (full_parity << stage);
@@ -422,7 +434,7 @@ __device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CU
     const ItemCoord c = decode_item(p, item);
     w.item = item;
     for (int q = 0; ok && q < kQTilesPerItem; ++q) {
-      ok = w.wait_warp(bar(kBarQEmpty + q), q_empty_parity, 100 + q);
+      ok = w.wait_issue(bar(kBarQEmpty + q), q_empty_parity, 100 + q);
       if (!ok) break;
       armed |= 1u << (kStages + q);
       armed_parity = (armed_parity & ~(1u << (kStages + q))) | (q_full_parity << (kStages + q));
@@ -477,12 +489,12 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
     w.item = item;
     w.tile = 0;
     // ---- tile 0 scores for both Q tiles
-    if (!(ok = w.wait_warp(bar(kBarKvFull + stage), full_parity, 200))) break;
+    if (!(ok = w.wait_issue(bar(kBarKvFull + stage), full_parity, 200))) break;
     {
       const uint32_t k_smem = smem_kv + stage * kTileBytes;
 #pragma unroll
       for (int q = 0; q < kQTilesPerItem; ++q) {
-        if (!(ok = w.wait_warp(bar(kBarQFull + q), q_full_parity, 201 + q))) break;
+        if (!(ok = w.wait_issue(bar(kBarQFull + q), q_full_parity, 201 + q))) break;
         tc_fence_after_sync();
         issue_qk(lead, tmem_base + q * kBlockN, smem_q + q * kTileBytes, k_smem);
         umma_commit_lead(lead, bar(kBarSFull + q));
@@ -496,7 +508,7 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
 
     for (int i = 0; ok && i < T; ++i) {
       w.tile = i;
-      if (!(ok = w.wait_warp(bar(kBarKvFull + stage), full_parity, 210))) break;
+      if (!(ok = w.wait_issue(bar(kBarKvFull + stage), full_parity, 210))) break;
       const uint32_t v_stage = stage;
       const uint32_t v_smem = smem_kv + v_stage * kTileBytes;
       advance();
@@ -508,19 +520,19 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
         if (q == 0 && has_next) {
           // the next K tile landed long ago; checking it here keeps the check off the
           // P -> PV -> QK -> S chain
-          if (!(ok = w.wait_warp(bar(kBarKvFull + stage), full_parity, 230))) break;
+          if (!(ok = w.wait_issue(bar(kBarKvFull + stage), full_parity, 230))) break;
         }
         if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 0);
         if (i == 0) {
           // the previous item's epilogue must have read O_q out before it is overwritten
-          if (!(ok = w.wait_warp(bar(kBarOFree + q), o_free_parity, 240 + q))) break;
+          if (!(ok = w.wait_issue(bar(kBarOFree + q), o_free_parity, 240 + q))) break;
         }
-        if (!(ok = w.wait_warp(bar(kBarPReady + q), p_parity, 220 + q))) break;
+        if (!(ok = w.wait_issue(bar(kBarPReady + q), p_parity, 220 + q))) break;
         tc_fence_after_sync();
         if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 1);
         issue_pv(lead, o_tmem, s_tmem, v_smem, 0, kPartAKSteps, /*accumulate_first=*/i > 0);
         if (kPartAChunks < 4) {
-          if (!(ok = w.wait_warp(bar(kBarPFull + q), p_parity, 225 + q))) break;
+          if (!(ok = w.wait_issue(bar(kBarPFull + q), p_parity, 225 + q))) break;
           tc_fence_after_sync();
           issue_pv(lead, o_tmem, s_tmem, v_smem, kPartAKSteps, kBlockN / 16, /*accumulate_first=*/true);
         }
@@ -655,6 +667,12 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
     for (int i = 0; i < T; ++i) {
       w.tile = i;
       if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 0);
+#if B200ATTN_S_WAIT_SLEEP_NS > 0
+      // The next scores cannot exist before this tile's PV and the next QK have run (>= ~1000
+      // clocks after P was published): stay off the sub-partition's issue port meanwhile, the
+      // other Q tile's softmax warp lives there too.
+      if (i > 0) __nanosleep(B200ATTN_S_WAIT_SLEEP_NS);
+#endif
       if (!w.wait_warp(bar(kBarSFull + q), s_parity, 300 + q)) return;
       s_parity ^= 1u;
       tc_fence_after_sync();
@@ -870,8 +888,13 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
   } else {
     reg_shrink<kRegsOther>();
     const uint32_t lead = (lane == 0) ? 1u : 0u;
+#ifdef B200ATTN_ISSUE_SINGLE_LANE
+    const bool runs = lead != 0;
+#else
+    const bool runs = true;
+#endif
     if (warp == 12) {
-      ws_mma_role(p, smem_q, smem_kv, bar0, tmem_base, lead, w);
+      if (runs) ws_mma_role(p, smem_q, smem_kv, bar0, tmem_base, lead, w);
     } else if (warp == 13) {
       if (lead) {
         tma_prefetch_desc(&tmap_q);
@@ -880,7 +903,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
       }
       __syncwarp();
       w.relaxed = true;
-      ws_load_role(p, &tmap_q, &tmap_k, &tmap_v, smem_q, smem_kv, bar0, lead, w);
+      if (runs) ws_load_role(p, &tmap_q, &tmap_k, &tmap_v, smem_q, smem_kv, bar0, lead, w);
     }
     __syncwarp();
   }

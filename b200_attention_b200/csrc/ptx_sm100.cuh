@@ -181,42 +181,7 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32
 }
 
 // Warp-uniform issue: every lane of the warp executes these with identical operands and only the
-// lane with `lead != 0` issues the instruction. Keeping the surrounding control flow and the
-// operand arithmetic uniform lets the assembler keep descriptors in uniform registers instead of
-// funnelling them through per-thread registers for a single active lane.
-__device__ __forceinline__ void umma_ss_lead(uint32_t lead, uint32_t d_tmem, uint32_t a_lo,
-                                             uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
-                                             uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p_acc, p_lead;\n\t"
-      ".reg .b64 da, db;\n\t"
-      "mov.b64 da, {%1, %2};\n\t"
-      "mov.b64 db, {%3, %4};\n\t"
-      "setp.ne.u32 p_acc, %6, 0;\n\t"
-      "setp.ne.u32 p_lead, %7, 0;\n\t"
-      "@p_lead tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p_acc;\n\t"
-      "}\n" ::"r"(d_tmem),
-      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(lead)
-      : "memory");
-}
-
-__device__ __forceinline__ void umma_ts_lead(uint32_t lead, uint32_t d_tmem, uint32_t a_tmem,
-                                             uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
-                                             uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p_acc, p_lead;\n\t"
-      ".reg .b64 db;\n\t"
-      "mov.b64 db, {%2, %3};\n\t"
-      "setp.ne.u32 p_acc, %5, 0;\n\t"
-      "setp.ne.u32 p_lead, %6, 0;\n\t"
-      "@p_lead tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p_acc;\n\t"
-      "}\n" ::"r"(d_tmem),
-      "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(lead)
-      : "memory");
-}
-
+// lane with `lead != 0` issues the instruction, so the surrounding control flow stays uniform.
 __device__ __forceinline__ void umma_commit_lead(uint32_t lead, uint32_t bar) {
   asm volatile(
       "{\n\t"
