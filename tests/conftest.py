@@ -14,7 +14,11 @@ def pytest_configure(config):
 
 @pytest.fixture(scope="session")
 def native_built():
-    """Build (if stale) and return the paths of the native libraries."""
-    from b200_attention_b200 import build
+    """Build (if stale) and return the paths of the native libraries. Device-side waits are
+    given a short limit for the test session, so a kernel that stalls fails in well under a
+    second per launch instead of holding the GPU."""
+    from b200_attention_b200 import _native, build
 
-    return build.build_all()
+    built = build.build_all()
+    _native.lib().b200attn_set_wait_limit_ms(400)
+    return built
