@@ -82,6 +82,11 @@ constexpr int kTraceTile0 = 8, kTraceTiles = 16;
 // ------------------------------------------------------------------------------------------
 // Bounded waits
 // ------------------------------------------------------------------------------------------
+// Suspend-time hint of the polls in the slow path of a wait (see mbarrier.try_wait).
+#ifndef B200ATTN_WAIT_HINT_NS
+#define B200ATTN_WAIT_HINT_NS 1000
+#endif
+
 struct WaitCtx {
   bool relaxed = false;  // role whose wake-up latency does not matter (may back off between polls)
   uint32_t abort_addr;  // shared-memory word: non-zero once any thread of the CTA gave up
@@ -112,7 +117,7 @@ struct WaitCtx {
   __device__ __forceinline__ bool wait_slow(uint32_t bar, uint32_t parity, int site) const {
     const uint64_t t0 = global_timer_ns();
     for (uint32_t n = 1;; ++n) {
-      if (mbar_try_wait(bar, parity, 1000)) return true;
+      if (mbar_try_wait(bar, parity, B200ATTN_WAIT_HINT_NS)) return true;
 #ifdef B200ATTN_SPIN_SLEEP
       if (relaxed) __nanosleep(B200ATTN_SPIN_SLEEP);
 #endif
