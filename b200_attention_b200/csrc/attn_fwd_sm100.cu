@@ -159,6 +159,7 @@ struct WaitCtx {
 // ------------------------------------------------------------------------------------------
 // MMA issue helpers (called by one thread)
 // ------------------------------------------------------------------------------------------
+// (No warp-level synchronisation in these helpers: the serial kernel calls them from one thread.)
 // S[128 x 128] = Q_tile * K_tile^T, eight K=16 steps over head_dim. Called by a whole warp with
 // uniform operands (so descriptors live in uniform registers); the lane with lead != 0 issues the
 // eight MMAs inside one branch. Measured at B4 H16 L8192: whole-warp roles 1311 TFLOPS, the
@@ -175,7 +176,6 @@ __device__ __forceinline__ void issue_qk(uint32_t lead, uint32_t s_tmem, uint32_
       umma_ss(s_tmem, a0 + off, hi, b0 + off, hi, kIdescQK, kk > 0 ? 1u : 0u);
     }
   }
-  __syncwarp();
 }
 
 // O[128 x 128] (+)= P[128 x 128 keys] * V_tile, K steps [kk_begin, kk_end). P is bf16 pairs in
@@ -194,7 +194,6 @@ __device__ __forceinline__ void issue_pv(uint32_t lead, uint32_t o_tmem, uint32_
       umma_ts(o_tmem, p_tmem + kk * 8, b0 + off, hi, kIdescPV, acc);
     }
   }
-  __syncwarp();
 }
 
 // ------------------------------------------------------------------------------------------
