@@ -79,6 +79,19 @@ constexpr int kTraceTile0 = 8, kTraceTiles = 16;
 #define B200ATTN_TRACE_EVENT_AFTER(p, role, item, tile, q, ev, dep) do { } while (0)
 #endif
 
+// Time budget instrumentation, compiled in only for B200ATTN_PROFILE builds: a role accumulates
+// clock64 deltas per category in registers and block 0 writes the totals once at the end, so the
+// measurement itself costs a clock read per boundary and nothing else.
+#ifdef B200ATTN_PROFILE
+#define PROF_DECL(n) long long prof_acc[n] = {}; long long prof_t = clock64()
+#define PROF_LAP(slot) do { const long long now_ = clock64(); prof_acc[slot] += now_ - prof_t; prof_t = now_; } while (0)
+#define PROF_FLUSH(p, base, n) do { if ((p).trace != nullptr && blockIdx.x == 0) { for (int i_ = 0; i_ < (n); ++i_) (p).trace[(base) + i_] = prof_acc[i_]; } } while (0)
+#else
+#define PROF_DECL(n) do { } while (0)
+#define PROF_LAP(slot) do { } while (0)
+#define PROF_FLUSH(p, base, n) do { } while (0)
+#endif
+
 // ------------------------------------------------------------------------------------------
 // Bounded waits
 // ------------------------------------------------------------------------------------------
@@ -488,6 +501,7 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
     }
   };
   const int T = p.kv_tiles;
+  PROF_DECL(8);  // 0 other, 1 wait V, 2 wait K, 3 wait P (+O_FREE), 4 issue PV, 5 issue QK, 6 commits
 
   for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
     w.item = item;
@@ -512,7 +526,9 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
 
     for (int i = 0; ok && i < T; ++i) {
       w.tile = i;
+      PROF_LAP(0);
       if (!(ok = w.wait_issue(bar(kBarKvFull + stage), full_parity, 210))) break;
+      PROF_LAP(1);
       const uint32_t v_stage = stage;
       const uint32_t v_smem = smem_kv + v_stage * kTileBytes;
       advance();
@@ -524,8 +540,11 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
         if (q == 0 && has_next) {
           // the next K tile landed long ago; checking it here keeps the check off the
           // P -> PV -> QK -> S chain
+          PROF_LAP(0);
           if (!(ok = w.wait_issue(bar(kBarKvFull + stage), full_parity, 230))) break;
+          PROF_LAP(2);
         }
+        PROF_LAP(0);
         if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 0);
         if (i == 0) {
           // the previous item's epilogue must have read O_q out before it is overwritten
@@ -533,8 +552,10 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
         }
         if (!(ok = w.wait_issue(bar(kBarPReady + q), p_parity, 220 + q))) break;
         tc_fence_after_sync();
+        PROF_LAP(3);
         if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 1);
         issue_pv(lead, o_tmem, s_tmem, v_smem, 0, kPartAKSteps, /*accumulate_first=*/i > 0);
+        PROF_LAP(4);
         if (kPartAChunks < 4) {
           if (!(ok = w.wait_issue(bar(kBarPFull + q), p_parity, 225 + q))) break;
           tc_fence_after_sync();
@@ -542,11 +563,14 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
         }
         if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 2);
         if (q == kQTilesPerItem - 1) umma_commit_lead(lead, bar(kBarKvEmpty + v_stage));
+        PROF_LAP(6);
         if (!has_next) {
           umma_commit_lead(lead, bar(kBarPvDone + q));
         } else {
           if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 3);
+          PROF_LAP(0);
           issue_qk(lead, s_tmem, smem_q + q * kTileBytes, smem_kv + stage * kTileBytes);
+          PROF_LAP(5);
           if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 4);
           umma_commit_lead(lead, bar(kBarSFull + q));
           if (i + 2 == T) umma_commit_lead(lead, bar(kBarQEmpty + q));
@@ -555,12 +579,15 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
             advance();
           }
         }
+        PROF_LAP(6);
         if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 5);
       }
       p_parity ^= 1u;
     }
     o_free_parity ^= 1u;
   }
+  PROF_LAP(0);
+  if (lead) PROF_FLUSH(p, 0, 8);
 
   if (!ok || w.aborted()) {
     // Leaving early: make sure nothing this warp issued is still running before TMEM goes.
@@ -655,6 +682,7 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
 #endif
   uint32_t s_parity = 0;
   uint32_t fin_free_parity = 1;  // passes on the fresh barrier: nothing to consume yet
+  PROF_DECL(8);  // 0 other, 1 wait S, 2 TMEM load, 3 exponentials + check, 4 store + signal
 
   for (int item = blockIdx.x; item < p.total_items; item += gridDim.x) {
     w.item = item;
@@ -677,9 +705,11 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
       // other Q tile's softmax warp lives there too.
       if (i > 0) __nanosleep(B200ATTN_S_WAIT_SLEEP_NS);
 #endif
+      PROF_LAP(0);
       if (!w.wait_warp(bar(kBarSFull + q), s_parity, 300 + q)) return;
       s_parity ^= 1u;
       tc_fence_after_sync();
+      PROF_LAP(1);
       if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 1);
 
       uint32_t s[4][32];
@@ -688,6 +718,7 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
       tmem_ld32(s_tmem + 64, s[2]);
       tmem_ld32(s_tmem + 96, s[3]);
       tmem_wait_ld();
+      PROF_LAP(2);
       if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 2);
       const bool tail = (i == T - 1 && tail_valid < kBlockN);
       if (tail) mask_tail(s, tail_valid);
@@ -754,6 +785,10 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
         sum_part_a = f2_hsum(sum_a, sum_b);
       }
       if (tr) B200ATTN_TRACE_EVENT_AFTER(p, q, item, i, 0, 3, sum_part_a);
+#ifdef B200ATTN_PROFILE
+      asm volatile("" ::"f"(sum_part_a), "r"(packed[kPartAChunks - 1][15]));
+#endif
+      PROF_LAP(3);
 
 #pragma unroll
       for (int c = 0; c < kPartAChunks; ++c) tmem_st16(p_tmem + c * 16, packed[c]);
@@ -761,6 +796,7 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kBarPReady + q));
+      PROF_LAP(4);
       if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 4);
 
       // part B
@@ -788,6 +824,8 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
     __syncwarp();
     if (lane == 0) mbar_arrive(bar(kBarFin + q));
   }
+  PROF_LAP(0);
+  if (warp_in_group == 0 && lane == 0) PROF_FLUSH(p, 8 + 8 * q, 8);
 }
 
 // ---- epilogue -------------------------------------------------------------------------------

@@ -209,7 +209,7 @@ int check_operand(const char* name, const b200attn_operand& t, int32_t batch, in
 }  // namespace host
 }  // namespace b200attn
 
-#ifdef B200ATTN_TRACE
+#if defined(B200ATTN_TRACE) || defined(B200ATTN_PROFILE)
 // Timeline studies only (never compiled into the shipped library): where block 0 records clock64.
 static long long* g_trace_buffer = nullptr;
 extern "C" B200ATTN_API void b200attn_debug_set_trace(void* device_buffer) {
@@ -273,7 +273,7 @@ int b200attn_forward(const b200attn_forward_args* a) {
   p.partial.lse = a->partial_lse;
   p.partial.merge = a->partial_merge != 0;
   p.partial.emit = a->partial_emit != 0;
-#ifdef B200ATTN_TRACE
+#if defined(B200ATTN_TRACE) || defined(B200ATTN_PROFILE)
   p.trace = g_trace_buffer;
 #endif
 
