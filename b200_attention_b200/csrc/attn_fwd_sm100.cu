@@ -83,8 +83,13 @@ constexpr int kTraceTile0 = 8, kTraceTiles = 16;
 // clock64 deltas per category in registers and block 0 writes the totals once at the end, so the
 // measurement itself costs a clock read per boundary and nothing else.
 #ifdef B200ATTN_PROFILE
-#define PROF_DECL(n) long long prof_acc[n] = {}; long long prof_t = clock64()
-#define PROF_LAP(slot) do { const long long now_ = clock64(); prof_acc[slot] += now_ - prof_t; prof_t = now_; } while (0)
+#define PROF_DECL(n) uint32_t prof_acc[n] = {}; uint32_t prof_t = uint32_t(clock())
+#ifdef B200ATTN_PROFILE_MMA
+// per-MMA laps only (slots >= 8); the coarse slots just restart the lap, to stay within registers
+#define PROF_LAP(slot) do { const uint32_t now_ = uint32_t(clock()); if ((slot) >= 8) prof_acc[(slot) - 8] += now_ - prof_t; prof_t = now_; } while (0)
+#else
+#define PROF_LAP(slot) do { const uint32_t now_ = uint32_t(clock()); prof_acc[slot] += now_ - prof_t; prof_t = now_; } while (0)
+#endif
 #define PROF_FLUSH(p, base, n) do { if ((p).trace != nullptr && blockIdx.x == 0) { for (int i_ = 0; i_ < (n); ++i_) (p).trace[(base) + i_] = prof_acc[i_]; } } while (0)
 #else
 #define PROF_DECL(n) do { } while (0)
@@ -150,13 +155,9 @@ struct WaitCtx {
     return wait_slow(bar, parity, site);
   }
 
-  // For the MMA and TMA roles: whole-warp (voted) or single-lane execution, chosen at compile time.
+  // For the MMA and TMA roles, which whole warps run with uniform control flow.
   __device__ __forceinline__ bool wait_issue(uint32_t bar, uint32_t parity, int site) const {
-#ifdef B200ATTN_ISSUE_SINGLE_LANE
-    return wait(bar, parity, site);
-#else
     return wait_warp(bar, parity, site);
-#endif
   }
 
   // For roles run by whole warps: every lane returns the same answer, so the warp stays
@@ -190,7 +191,6 @@ __device__ __forceinline__ void issue_qk(uint32_t lead, uint32_t s_tmem, uint32_
     }
   }
 }
-
 // O[128 x 128] (+)= P[128 x 128 keys] * V_tile, K steps [kk_begin, kk_end). P is bf16 pairs in
 // TMEM, 8 columns per K step starting at p_tmem.
 __device__ __forceinline__ void issue_pv(uint32_t lead, uint32_t o_tmem, uint32_t p_tmem,
@@ -339,9 +339,6 @@ __device__ __forceinline__ float row_max(const uint32_t (&s)[4][32]) {
 // ==========================================================================================
 // Warp-specialised persistent kernel
 // ==========================================================================================
-#ifndef B200ATTN_KV_STAGES
-#define B200ATTN_KV_STAGES 4
-#endif
 // Of every 16 exponentials, this many are computed with the FMA-pipe polynomial instead of the
 // MUFU unit. 0 is fastest while the softmax warps are bound by instruction issue rather than by
 // MUFU throughput (measured: 0 -> 1282, 4 -> 1237, 8 -> 1140 TFLOPS at B4 H16 L8192).
@@ -369,7 +366,8 @@ constexpr int kPartAKSteps = kPartAChunks * 2;  // K = 16 keys per MMA step
 #ifndef B200ATTN_S_WAIT_SLEEP_NS
 #define B200ATTN_S_WAIT_SLEEP_NS 0
 #endif
-constexpr int kStages = B200ATTN_KV_STAGES;
+constexpr int kPairSlots = 2;                 // ring of (V, K) pairs
+constexpr int kPairBytes = 2 * kTileBytes;    // V tile, then K tile
 constexpr int kWsThreads = 512;
 constexpr int kRegsSoftmax = 192;
 constexpr int kRegsEpilogue = 80;
@@ -386,9 +384,9 @@ enum WsBarrier : int {
   kBarFinFree = 14, // +q   epilogue (4 warps) -> softmax: final (max, sum) consumed
   kBarOFree = 16,   // +q   epilogue (4 warps) -> MMA: O_q read out, the next item may overwrite it
   kBarDrain = 18,   //      MMA -> MMA       used only when leaving early
-  kBarKvFull = 20,  // +stage
-  kBarKvEmpty = 20 + kStages,
-  kNumWsBarriers = 20 + 2 * kStages
+  kBarPairFull = 20,   // +slot  TMA -> MMA   the pair's V and K tiles landed
+  kBarPairEmpty = 22,  // +slot  MMA -> TMA   PV and QK that read the pair finished
+  kNumWsBarriers = 24
 };
 
 struct alignas(16) WsAux {
@@ -399,7 +397,7 @@ struct alignas(16) WsAux {
   uint32_t abort_flag;
 };
 
-constexpr int kWsSmemBytes = kQTilesPerItem * kTileBytes + kStages * kTileBytes + int(sizeof(WsAux));
+constexpr int kWsSmemBytes = kQTilesPerItem * kTileBytes + kPairSlots * kPairBytes + int(sizeof(WsAux));
 
 struct ItemCoord {
   int b, h, row0;
@@ -426,7 +424,13 @@ __device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CU
                              const CUtensorMap* tv, uint32_t smem_q, uint32_t smem_kv,
                              uint32_t bar0, uint32_t lead, WaitCtx& w) {
   // Run by the whole warp with uniform control flow; `lead` marks the one lane that issues.
-  uint32_t stage = 0, empty_parity = 1;  // parity 1 passes on a fresh barrier
+  //
+  // K/V travel in pairs: pair j holds V of tile j-1 and K of tile j (tiles numbered through all
+  // of this CTA's items), because that is what the MMA warp consumes together: PV of tile j-1
+  // and then QK of tile j. One "full" and one "empty" barrier phase per pair halves the
+  // barrier work of the MMA warp against one phase per tile. The first pair has no V, the last
+  // one no K.
+  uint32_t slot = 0, empty_parity = 1;  // parity 1 passes on a fresh barrier
   uint32_t q_empty_parity = 1;
   // For the early-exit path: which "full" barriers were armed, and with which parity last.
   uint32_t armed = 0, armed_parity = 0;
@@ -434,47 +438,70 @@ __device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CU
   bool ok = true;
 
   auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
-  auto push_kv = [&](const CUtensorMap* map, int row, int h, int b, int site) -> bool {
-    if (!w.wait_issue(bar(kBarKvEmpty + stage), empty_parity, site)) return false;
+  auto push_pair = [&](bool has_v, int v_row, const ItemCoord& vc, bool has_k, int k_row,
+                       const ItemCoord& kc, int site) -> bool {
+    if (!w.wait_issue(bar(kBarPairEmpty + slot), empty_parity, site)) return false;
     const uint32_t full_parity = empty_parity ^ 1u;
-    armed |= 1u << stage;
-    armed_parity = (armed_parity & ~(1u << stage)) | (full_parity << stage);
-    load_tile(lead, smem_kv + stage * kTileBytes, map, row, h, b, bar(kBarKvFull + stage));
-    if (++stage == kStages) {
-      stage = 0;
-      empty_parity ^= 1u;
+    armed |= 1u << slot;
+    armed_parity = (armed_parity & ~(1u << slot)) | (full_parity << slot);
+    const uint32_t full = bar(kBarPairFull + slot);
+    const uint32_t dst = smem_kv + slot * kPairBytes;
+    mbar_arrive_expect_tx_lead(lead, full, (has_v ? kTileBytes : 0) + (has_k ? kTileBytes : 0));
+    if (has_v) {
+      tma_load_4d_lead(lead, dst, tv, 0, v_row, vc.h, vc.b, full);
+      tma_load_4d_lead(lead, dst + kBoxBytes, tv, 64, v_row, vc.h, vc.b, full);
     }
+    if (has_k) {
+      tma_load_4d_lead(lead, dst + kTileBytes, tk, 0, k_row, kc.h, kc.b, full);
+      tma_load_4d_lead(lead, dst + kTileBytes + kBoxBytes, tk, 64, k_row, kc.h, kc.b, full);
+    }
+    slot ^= 1u;
+    if (slot == 0) empty_parity ^= 1u;
     return true;
   };
 
+  const int T = p.kv_tiles;
+  bool first = true;
   for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
     const ItemCoord c = decode_item(p, item);
     w.item = item;
+    w.tile = 0;
+    if (first) {
+      ok = push_pair(false, 0, c, true, 0, c, 110);  // K_0 of the first item travels alone
+      first = false;
+      if (!ok) break;
+    }
     for (int q = 0; ok && q < kQTilesPerItem; ++q) {
       ok = w.wait_issue(bar(kBarQEmpty + q), q_empty_parity, 100 + q);
       if (!ok) break;
-      armed |= 1u << (kStages + q);
-      armed_parity = (armed_parity & ~(1u << (kStages + q))) | (q_full_parity << (kStages + q));
+      armed |= 1u << (kPairSlots + q);
+      armed_parity = (armed_parity & ~(1u << (kPairSlots + q))) | (q_full_parity << (kPairSlots + q));
       load_tile(lead, smem_q + q * kTileBytes, tq, c.row0 + q * kBlockM, c.h, c.b,
                 bar(kBarQFull + q));
-      if (q == 0) ok = push_kv(tk, 0, c.h, c.b, 110);  // K_0 right behind Q_0
     }
     q_empty_parity ^= 1u;
     q_full_parity ^= 1u;
-    for (int i = 0; ok && i < p.kv_tiles; ++i) {
+    for (int i = 0; ok && i < T; ++i) {
       w.tile = i;
-      if (i > 0) ok = push_kv(tk, i * kBlockN, c.h, c.b, 111);
-      if (ok) ok = push_kv(tv, i * kBlockN, c.h, c.b, 112);
+      if (i + 1 < T) {
+        ok = push_pair(true, i * kBlockN, c, true, (i + 1) * kBlockN, c, 111);
+      } else {
+        // the last V of this item shares its pair with K_0 of the CTA's next item, if any
+        const int next_item = item + int(gridDim.x);
+        const bool has_next_item = next_item < p.total_items;
+        ok = push_pair(true, i * kBlockN, c, has_next_item, 0,
+                       has_next_item ? decode_item(p, next_item) : c, 112);
+      }
     }
   }
 
   if (!ok || w.aborted()) {
     // Leaving early: wait (bounded) for every copy still in flight, so no TMA write lands in
     // shared memory after the CTA is gone.
-    for (int s = 0; s < kStages + kQTilesPerItem; ++s) {
+    for (int s = 0; s < kPairSlots + kQTilesPerItem; ++s) {
       if (!((armed >> s) & 1u)) continue;
       const uint32_t b =
-          (s < kStages) ? bar(kBarKvFull + s) : bar(kBarQFull + (s - kStages));
+          (s < kPairSlots) ? bar(kBarPairFull + s) : bar(kBarQFull + (s - kPairSlots));
       const uint64_t t0 = global_timer_ns();
       while (!mbar_try_wait(b, (armed_parity >> s) & 1u, 1000)) {
         if (global_timer_ns() - t0 > w.limit_ns) break;
@@ -488,62 +515,61 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
                             uint32_t tmem_base, uint32_t lead, WaitCtx& w) {
   // Run by the whole warp with uniform control flow; `lead` marks the one lane that issues.
   auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
-  uint32_t stage = 0, full_parity = 0;
+  // K/V arrive in pairs (V of one tile with K of the next): see ws_load_role.
+  uint32_t slot = 0, full_parity = 0;  // the pair to wait for next
   uint32_t q_full_parity = 0;
   uint32_t p_parity = 0;       // kBarPReady / kBarPFull: both Q tiles see one phase per K/V tile
   uint32_t o_free_parity = 1;  // passes on the fresh barrier: both accumulators start out free
   bool ok = true;
+  // The pair in use is always the one waited for last, slot ^ 1. After the first item, K_0 of
+  // an item has already arrived with the last V of the item before.
+  bool k_ready = false;
 
-  auto advance = [&]() {
-    if (++stage == kStages) {
-      stage = 0;
-      full_parity ^= 1u;
-    }
-  };
   const int T = p.kv_tiles;
-  PROF_DECL(8);  // 0 other, 1 wait V, 2 wait K, 3 wait P (+O_FREE), 4 issue PV, 5 issue QK, 6 commits
+  PROF_DECL(8);  // 0 other, 1 wait pair, 3 wait P (+O_FREE), 4 issue PV, 5 issue QK, 6 commits
 
   for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
     w.item = item;
     w.tile = 0;
     // ---- tile 0 scores for both Q tiles
-    if (!(ok = w.wait_issue(bar(kBarKvFull + stage), full_parity, 200))) break;
-    {
-      const uint32_t k_smem = smem_kv + stage * kTileBytes;
-#pragma unroll
-      for (int q = 0; q < kQTilesPerItem; ++q) {
-        if (!(ok = w.wait_issue(bar(kBarQFull + q), q_full_parity, 201 + q))) break;
-        tc_fence_after_sync();
-        issue_qk(lead, tmem_base + q * kBlockN, smem_q + q * kTileBytes, k_smem);
-        umma_commit_lead(lead, bar(kBarSFull + q));
-        if (T == 1) umma_commit_lead(lead, bar(kBarQEmpty + q));
-      }
-      if (!ok) break;
-      umma_commit_lead(lead, bar(kBarKvEmpty + stage));
-      advance();
+    if (!k_ready) {
+      if (!(ok = w.wait_issue(bar(kBarPairFull + slot), full_parity, 200))) break;
+      slot ^= 1u;
+      if (slot == 0) full_parity ^= 1u;
+      k_ready = true;
     }
+    {
+      const uint32_t k_smem = smem_kv + (slot ^ 1u) * kPairBytes + kTileBytes;
+#pragma unroll
+    for (int q = 0; q < kQTilesPerItem; ++q) {
+      if (!(ok = w.wait_issue(bar(kBarQFull + q), q_full_parity, 201 + q))) break;
+      tc_fence_after_sync();
+      issue_qk(lead, tmem_base + q * kBlockN, smem_q + q * kTileBytes, k_smem);
+      umma_commit_lead(lead, bar(kBarSFull + q));
+      if (T == 1) umma_commit_lead(lead, bar(kBarQEmpty + q));
+    }
+    }
+    if (!ok) break;
+    // also covers the PV of the previous item that read the V half of this pair
+    umma_commit_lead(lead, bar(kBarPairEmpty + (slot ^ 1u)));
     q_full_parity ^= 1u;
 
     for (int i = 0; ok && i < T; ++i) {
       w.tile = i;
       PROF_LAP(0);
-      if (!(ok = w.wait_issue(bar(kBarKvFull + stage), full_parity, 210))) break;
+      // V_i and K_{i+1} (or K_0 of this CTA's next item) in one phase
+      if (!(ok = w.wait_issue(bar(kBarPairFull + slot), full_parity, 210))) break;
       PROF_LAP(1);
-      const uint32_t v_stage = stage;
-      const uint32_t v_smem = smem_kv + v_stage * kTileBytes;
-      advance();
+      const uint32_t v_smem = smem_kv + slot * kPairBytes;
+      const uint32_t k_smem = v_smem + kTileBytes;
+      const uint32_t pair_empty = bar(kBarPairEmpty + slot);
+      slot ^= 1u;
+      if (slot == 0) full_parity ^= 1u;
       const bool has_next = (i + 1 < T);
 #pragma unroll
       for (int q = 0; q < kQTilesPerItem; ++q) {
         const uint32_t s_tmem = tmem_base + q * kBlockN;
         const uint32_t o_tmem = tmem_base + kQTilesPerItem * kBlockN + q * kHeadDim;
-        if (q == 0 && has_next) {
-          // the next K tile landed long ago; checking it here keeps the check off the
-          // P -> PV -> QK -> S chain
-          PROF_LAP(0);
-          if (!(ok = w.wait_issue(bar(kBarKvFull + stage), full_parity, 230))) break;
-          PROF_LAP(2);
-        }
         PROF_LAP(0);
         if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 0);
         if (i == 0) {
@@ -554,30 +580,49 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
         tc_fence_after_sync();
         PROF_LAP(3);
         if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 1);
+#if B200ATTN_PROFILE_MMA == 1
+        // one lap per MMA: slots 8..15
+#pragma unroll
+        for (int kk = 0; kk < kBlockN / 16; ++kk) {
+          issue_pv(lead, o_tmem, s_tmem, v_smem, kk, kk + 1, /*accumulate_first=*/i > 0 || kk > 0);
+          PROF_LAP(8 + kk);
+        }
+#else
         issue_pv(lead, o_tmem, s_tmem, v_smem, 0, kPartAKSteps, /*accumulate_first=*/i > 0);
         PROF_LAP(4);
+#endif
         if (kPartAChunks < 4) {
           if (!(ok = w.wait_issue(bar(kBarPFull + q), p_parity, 225 + q))) break;
           tc_fence_after_sync();
           issue_pv(lead, o_tmem, s_tmem, v_smem, kPartAKSteps, kBlockN / 16, /*accumulate_first=*/true);
         }
         if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 2);
-        if (q == kQTilesPerItem - 1) umma_commit_lead(lead, bar(kBarKvEmpty + v_stage));
-        PROF_LAP(6);
         if (!has_next) {
           umma_commit_lead(lead, bar(kBarPvDone + q));
         } else {
           if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 3);
           PROF_LAP(0);
-          issue_qk(lead, s_tmem, smem_q + q * kTileBytes, smem_kv + stage * kTileBytes);
+#if B200ATTN_PROFILE_MMA == 2
+          // one lap per MMA: slots 8..15
+          {
+            constexpr uint32_t hi = umma_desc_hi_sw128(kSwizzleGroupBytes);
+            const uint32_t a0 = umma_desc_lo(smem_q + q * kTileBytes, 0);
+            const uint32_t b0 = umma_desc_lo(k_smem, 0);
+#pragma unroll
+            for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+              const uint32_t off = uint32_t(((kk >> 2) * kBoxBytes + (kk & 3) * 32) >> 4);
+              if (lead) umma_ss(s_tmem, a0 + off, hi, b0 + off, hi, kIdescQK, kk > 0 ? 1u : 0u);
+              PROF_LAP(8 + kk);
+            }
+          }
+#else
+          issue_qk(lead, s_tmem, smem_q + q * kTileBytes, k_smem);
           PROF_LAP(5);
+#endif
           if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 4);
           umma_commit_lead(lead, bar(kBarSFull + q));
           if (i + 2 == T) umma_commit_lead(lead, bar(kBarQEmpty + q));
-          if (q == kQTilesPerItem - 1) {
-            umma_commit_lead(lead, bar(kBarKvEmpty + stage));
-            advance();
-          }
+          if (q == kQTilesPerItem - 1) umma_commit_lead(lead, pair_empty);
         }
         PROF_LAP(6);
         if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 5);
@@ -587,7 +632,12 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
     o_free_parity ^= 1u;
   }
   PROF_LAP(0);
+#ifndef B200ATTN_PROFILE_MMA
   if (lead) PROF_FLUSH(p, 0, 8);
+#endif
+#ifdef B200ATTN_PROFILE_MMA
+  if (lead) { for (int i_ = 0; i_ < 8; ++i_) if (p.trace != nullptr && blockIdx.x == 0) p.trace[24 + 8 * (B200ATTN_PROFILE_MMA - 1) + i_] = prof_acc[i_]; }
+#endif
 
   if (!ok || w.aborted()) {
     // Leaving early: make sure nothing this warp issued is still running before TMEM goes.
@@ -714,13 +764,14 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
 
       uint32_t s[4][32];
       tmem_ld32(s_tmem + 0, s[0]);
+      tmem_wait_ld();  // chunk 0 alone, so that its exponentials overlap the other three loads
       tmem_ld32(s_tmem + 32, s[1]);
       tmem_ld32(s_tmem + 64, s[2]);
       tmem_ld32(s_tmem + 96, s[3]);
-      tmem_wait_ld();
       PROF_LAP(2);
       if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 2);
       const bool tail = (i == T - 1 && tail_valid < kBlockN);
+      if (tail || i == 0 || kPartAChunks < 4) tmem_wait_ld();  // these paths look at all chunks at once
       if (tail) mask_tail(s, tail_valid);
 
       uint32_t packed[kPartAChunks][16];
@@ -736,6 +787,7 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
 #pragma unroll
         for (int c = 0; c < kPartAChunks; ++c) {
           exp_chunk(s[c], scale2, neg_m2, packed[c], sum_a, sum_b);
+          if (c == 0) tmem_wait_ld();
 #ifdef B200ATTN_TRACE_FINE
           if (tr && c == 0) B200ATTN_TRACE_EVENT_AFTER(p, q, item, i, 0, 7, __uint_as_float(packed[0][15]));
           if (tr && c == 1) B200ATTN_TRACE_EVENT_AFTER(p, q, item, i, 0, 0, __uint_as_float(packed[1][15]));
@@ -795,7 +847,7 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(kBarPReady + q));
+      mbar_arrive_lead(lane == 0 ? 1u : 0u, bar(kBarPReady + q));
       PROF_LAP(4);
       if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 4);
 
@@ -873,7 +925,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
   const uint32_t smem_q = smem_u32(smem);
   const uint32_t smem_kv = smem_q + kQTilesPerItem * kTileBytes;
-  WsAux* aux = reinterpret_cast<WsAux*>(smem + (kQTilesPerItem + kStages) * kTileBytes);
+  WsAux* aux = reinterpret_cast<WsAux*>(smem + kQTilesPerItem * kTileBytes + kPairSlots * kPairBytes);
   const uint32_t bar0 = smem_u32(&aux->bar[0]);
 
   WaitCtx w;
@@ -902,9 +954,9 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
       }
       mbar_init(bar0 + 8u * kBarDrain, 1);
       mbar_init(bar0 + 8u * (kBarDrain + 1), 1);
-      for (int s = 0; s < kStages; ++s) {
-        mbar_init(bar0 + 8u * (kBarKvFull + s), 1);
-        mbar_init(bar0 + 8u * (kBarKvEmpty + s), 1);
+      for (int s = 0; s < kPairSlots; ++s) {
+        mbar_init(bar0 + 8u * (kBarPairFull + s), 1);
+        mbar_init(bar0 + 8u * (kBarPairEmpty + s), 1);
       }
       mbar_init_fence();
       fence_proxy_async_smem();
@@ -930,13 +982,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
   } else {
     reg_shrink<kRegsOther>();
     const uint32_t lead = (lane == 0) ? 1u : 0u;
-#ifdef B200ATTN_ISSUE_SINGLE_LANE
-    const bool runs = lead != 0;
-#else
-    const bool runs = true;
-#endif
     if (warp == 12) {
-      if (runs) ws_mma_role(p, smem_q, smem_kv, bar0, tmem_base, lead, w);
+      ws_mma_role(p, smem_q, smem_kv, bar0, tmem_base, lead, w);
     } else if (warp == 13) {
       if (lead) {
         tma_prefetch_desc(&tmap_q);
@@ -945,7 +992,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
       }
       __syncwarp();
       w.relaxed = true;
-      if (runs) ws_load_role(p, &tmap_q, &tmap_k, &tmap_v, smem_q, smem_kv, bar0, lead, w);
+      ws_load_role(p, &tmap_q, &tmap_k, &tmap_v, smem_q, smem_kv, bar0, lead, w);
     }
     __syncwarp();
   }

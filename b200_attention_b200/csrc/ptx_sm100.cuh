@@ -44,6 +44,18 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
 
+// Arrival by the lane with lead != 0 only, by predication (no branch).
+__device__ __forceinline__ void mbar_arrive_lead(uint32_t lead, uint32_t bar) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p_lead;\n\t"
+      "setp.ne.u32 p_lead, %1, 0;\n\t"
+      "@p_lead mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];\n\t"
+      "}\n" ::"r"(bar),
+      "r"(lead)
+      : "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.release.cta.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar),
                "r"(bytes)

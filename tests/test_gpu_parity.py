@@ -65,7 +65,7 @@ SHAPES = [
     (1, 1, 128, 128),      # half a work item, one K/V tile
     (1, 1, 256, 128),      # one work item, one tile
     (1, 1, 256, 256),      # two tiles: ring prefill only
-    (1, 2, 256, 640),      # five tiles: ring refill with 4 stages
+    (1, 2, 256, 640),      # five tiles: the two-slot (V, K) pair ring refills
     (2, 3, 512, 384),
     (1, 2, 200, 333),      # ragged in both lengths
     (1, 1, 1, 1),          # degenerate
