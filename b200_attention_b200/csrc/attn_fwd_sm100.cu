@@ -101,9 +101,6 @@ constexpr int kTraceTile0 = 8, kTraceTiles = 16;
 // Bounded waits
 // ------------------------------------------------------------------------------------------
 // Suspend-time hint of the polls in the slow path of a wait (see mbarrier.try_wait).
-#ifndef B200ATTN_ELECT_ISSUE
-#define B200ATTN_ELECT_ISSUE 0
-#endif
 #ifndef B200ATTN_WAIT_HINT_NS
 #define B200ATTN_WAIT_HINT_NS 1000
 #endif
@@ -158,13 +155,9 @@ struct WaitCtx {
     return wait_slow(bar, parity, site);
   }
 
-  // For the MMA and TMA roles: run by one elected thread, or by whole warps with uniform control flow.
+  // For the MMA and TMA roles, which whole warps run with uniform control flow.
   __device__ __forceinline__ bool wait_issue(uint32_t bar, uint32_t parity, int site) const {
-#if B200ATTN_ELECT_ISSUE
-    return wait(bar, parity, site);
-#else
     return wait_warp(bar, parity, site);
-#endif
   }
 
   // For roles run by whole warps: every lane returns the same answer, so the warp stays
@@ -377,11 +370,8 @@ constexpr int kPairSlots = 2;                 // ring of (V, K) pairs
 constexpr int kPairBytes = 2 * kTileBytes;    // V tile, then K tile
 constexpr int kWsThreads = 512;
 constexpr int kRegsSoftmax = 192;
-#ifndef B200ATTN_REGS_EPILOGUE
-#define B200ATTN_REGS_EPILOGUE 80
-#endif
-constexpr int kRegsEpilogue = B200ATTN_REGS_EPILOGUE;
-constexpr int kRegsOther = 128 - kRegsEpilogue;  // 2 * 192 + epilogue + other = 4 * 128
+constexpr int kRegsEpilogue = 80;
+constexpr int kRegsOther = 48;
 
 enum WsBarrier : int {
   kBarQFull = 0,    // +q   TMA -> MMA       Q tile q landed
@@ -991,19 +981,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
     ws_epilogue_role(p, aux, bar0, tmem_base, warp & 3, lane, w);
   } else {
     reg_shrink<kRegsOther>();
-#if B200ATTN_ELECT_ISSUE
-    if (warp == 12) {
-      if (elect_one()) ws_mma_role(p, smem_q, smem_kv, bar0, tmem_base, 1u, w);
-    } else if (warp == 13) {
-      if (elect_one()) {
-        tma_prefetch_desc(&tmap_q);
-        tma_prefetch_desc(&tmap_k);
-        tma_prefetch_desc(&tmap_v);
-        w.relaxed = true;
-        ws_load_role(p, &tmap_q, &tmap_k, &tmap_v, smem_q, smem_kv, bar0, 1u, w);
-      }
-    }
-#else
     const uint32_t lead = (lane == 0) ? 1u : 0u;
     if (warp == 12) {
       ws_mma_role(p, smem_q, smem_kv, bar0, tmem_base, lead, w);
@@ -1017,7 +994,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
       w.relaxed = true;
       ws_load_role(p, &tmap_q, &tmap_k, &tmap_v, smem_q, smem_kv, bar0, lead, w);
     }
-#endif
     __syncwarp();
   }
 
