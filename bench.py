@@ -167,6 +167,13 @@ def cpu_sdpa_sample(b, h, lq, lk, budget_s: float, max_heads: int | None = None)
 
     from oracle import sdpa_oracle as O
 
+    # torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every host core it may run on
+    try:
+        usable = len(os.sched_getaffinity(0))
+    except AttributeError:
+        usable = os.cpu_count() or 1
+    if torch.get_num_threads() < usable:
+        torch.set_num_threads(usable)
     cores = torch.get_num_threads()
     g = torch.Generator().manual_seed(0)
     total = b * h if max_heads is None else min(b * h, max_heads)
