@@ -18,19 +18,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-// True in exactly one lane of a fully converged warp.
-__device__ __forceinline__ bool elect_one() {
-  uint32_t is_leader = 0;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p_el;\n\t"
-      "elect.sync _|p_el, 0xffffffff;\n\t"
-      "selp.u32 %0, 1, 0, p_el;\n\t"
-      "}\n"
-      : "=r"(is_leader));
-  return is_leader != 0;
-}
-
 // ----------------------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t arrivals) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(arrivals) : "memory");
@@ -54,12 +41,6 @@ __device__ __forceinline__ void mbar_arrive_lead(uint32_t lead, uint32_t bar) {
       "}\n" ::"r"(bar),
       "r"(lead)
       : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.release.cta.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar),
-               "r"(bytes)
-               : "memory");
 }
 
 // One poll; the hardware may suspend the thread for up to `hint_ns` before answering.
@@ -97,17 +78,6 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 }
 
 // ----------------------------------------------------------------------------- TMA
-// 4-D tiled load: coordinates are (innermost .. outermost) = (c0, c1, c2, c3).
-// c0 * element size must be a multiple of 16 bytes.
-__device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap, int c0, int c1,
-                                            int c2, int c3, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cta.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%2, %3, %4, %5}], [%6];\n" ::"r"(dst_smem),
-      "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
-      : "memory");
-}
-
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];\n" ::"l"(tmap) : "memory");
 }
@@ -137,11 +107,8 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 //   bits 32..45  stride-dimension byte offset >> 4
 //   bits 46..47  version (1)
 //   bits 61..63  layout type (2 = 128-byte swizzle)
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                    uint32_t sbo_bytes) {
-  return (uint64_t((smem_addr & 0x3FFFFu) >> 4)) | (uint64_t((lbo_bytes >> 4) & 0x3FFFu) << 16) |
-         (uint64_t((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
-}
+// The kernels keep the two 32-bit halves apart (umma_desc_lo / umma_desc_hi_sw128 below): the
+// high half is a compile-time constant and the low half is one add away from the tile base.
 
 // Instruction descriptor for kind::f16, bf16 x bf16 -> fp32, A K-major.
 //   bit 4: D is fp32; bit 7: A is bf16; bit 10: B is bf16; bit 16: B is MN-major;
@@ -217,6 +184,8 @@ __device__ __forceinline__ void mbar_arrive_expect_tx_lead(uint32_t lead, uint32
       : "memory");
 }
 
+// 4-D tiled load: coordinates are (innermost .. outermost) = (c0, c1, c2, c3).
+// c0 * element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_4d_lead(uint32_t lead, uint32_t dst_smem, const void* tmap,
                                                  int c0, int c1, int c2, int c3, uint32_t bar) {
   asm volatile(
@@ -316,12 +285,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-__device__ __forceinline__ float lg2_approx(float x) {
-  float y;
-  asm("lg2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-  return y;
-}
-
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float y;
   asm("max.f32 %0, %1, %2, %3;\n" : "=f"(y) : "f"(a), "f"(b), "f"(c));
@@ -371,12 +334,6 @@ __device__ __forceinline__ f2 f2_add_rm(f2 a, f2 b) {
 __device__ __forceinline__ f2 f2_sub(f2 a, f2 b) {
   f2 r;
   asm("sub.rn.f32x2 %0, %1, %2;\n" : "=l"(r.bits) : "l"(a.bits), "l"(b.bits));
-  return r;
-}
-
-__device__ __forceinline__ f2 f2_mul(f2 a, f2 b) {
-  f2 r;
-  asm("mul.rn.f32x2 %0, %1, %2;\n" : "=l"(r.bits) : "l"(a.bits), "l"(b.bits));
   return r;
 }
 
