@@ -84,12 +84,7 @@ constexpr int kTraceTile0 = 8, kTraceTiles = 16;
 // measurement itself costs a clock read per boundary and nothing else.
 #ifdef B200ATTN_PROFILE
 #define PROF_DECL(n) uint32_t prof_acc[n] = {}; uint32_t prof_t = uint32_t(clock())
-#ifdef B200ATTN_PROFILE_MMA
-// per-MMA laps only (slots >= 8); the coarse slots just restart the lap, to stay within registers
-#define PROF_LAP(slot) do { const uint32_t now_ = uint32_t(clock()); if ((slot) >= 8) prof_acc[(slot) - 8] += now_ - prof_t; prof_t = now_; } while (0)
-#else
 #define PROF_LAP(slot) do { const uint32_t now_ = uint32_t(clock()); prof_acc[slot] += now_ - prof_t; prof_t = now_; } while (0)
-#endif
 #define PROF_FLUSH(p, base, n) do { if ((p).trace != nullptr && blockIdx.x == 0) { for (int i_ = 0; i_ < (n); ++i_) (p).trace[(base) + i_] = prof_acc[i_]; } } while (0)
 #else
 #define PROF_DECL(n) do { } while (0)
@@ -106,7 +101,6 @@ constexpr int kTraceTile0 = 8, kTraceTiles = 16;
 #endif
 
 struct WaitCtx {
-  bool relaxed = false;  // role whose wake-up latency does not matter (may back off between polls)
   uint32_t abort_addr;  // shared-memory word: non-zero once any thread of the CTA gave up
   int32_t* status;
   uint64_t limit_ns;
@@ -136,9 +130,6 @@ struct WaitCtx {
     const uint64_t t0 = global_timer_ns();
     for (uint32_t n = 1;; ++n) {
       if (mbar_try_wait(bar, parity, B200ATTN_WAIT_HINT_NS)) return true;
-#ifdef B200ATTN_SPIN_SLEEP
-      if (relaxed) __nanosleep(B200ATTN_SPIN_SLEEP);
-#endif
       if ((n & 7u) == 0) {
         if (aborted()) return false;
         if (global_timer_ns() - t0 > limit_ns) {
@@ -311,17 +302,6 @@ __device__ __forceinline__ void mask_tail(uint32_t (&s)[4][32], int valid) {
 }
 
 __device__ __forceinline__ float row_max(const uint32_t (&s)[4][32]) {
-#ifdef B200ATTN_MAX2
-  float v[8];
-#pragma unroll
-  for (int k = 0; k < 8; ++k) v[k] = kNegInf;
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) v[j & 7] = fmaxf(v[j & 7], __uint_as_float(s[c][j]));
-  }
-  return fmaxf(fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3])), fmaxf(fmaxf(v[4], v[5]), fmaxf(v[6], v[7])));
-#endif
   float m0 = kNegInf, m1 = kNegInf, m2 = kNegInf, m3 = kNegInf;
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
@@ -363,9 +343,6 @@ __device__ __forceinline__ float row_max(const uint32_t (&s)[4][32]) {
 constexpr int kPartAChunks = B200ATTN_PART_A_CHUNKS;
 constexpr int kPartAKSteps = kPartAChunks * 2;  // K = 16 keys per MMA step
 
-#ifndef B200ATTN_S_WAIT_SLEEP_NS
-#define B200ATTN_S_WAIT_SLEEP_NS 0
-#endif
 constexpr int kPairSlots = 2;                 // ring of (V, K) pairs
 constexpr int kPairBytes = 2 * kTileBytes;    // V tile, then K tile
 constexpr int kWsThreads = 512;
@@ -580,17 +557,8 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
         tc_fence_after_sync();
         PROF_LAP(3);
         if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 1);
-#if B200ATTN_PROFILE_MMA == 1
-        // one lap per MMA: slots 8..15
-#pragma unroll
-        for (int kk = 0; kk < kBlockN / 16; ++kk) {
-          issue_pv(lead, o_tmem, s_tmem, v_smem, kk, kk + 1, /*accumulate_first=*/i > 0 || kk > 0);
-          PROF_LAP(8 + kk);
-        }
-#else
         issue_pv(lead, o_tmem, s_tmem, v_smem, 0, kPartAKSteps, /*accumulate_first=*/i > 0);
         PROF_LAP(4);
-#endif
         if (kPartAChunks < 4) {
           if (!(ok = w.wait_issue(bar(kBarPFull + q), p_parity, 225 + q))) break;
           tc_fence_after_sync();
@@ -602,23 +570,8 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
         } else {
           if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 3);
           PROF_LAP(0);
-#if B200ATTN_PROFILE_MMA == 2
-          // one lap per MMA: slots 8..15
-          {
-            constexpr uint32_t hi = umma_desc_hi_sw128(kSwizzleGroupBytes);
-            const uint32_t a0 = umma_desc_lo(smem_q + q * kTileBytes, 0);
-            const uint32_t b0 = umma_desc_lo(k_smem, 0);
-#pragma unroll
-            for (int kk = 0; kk < kHeadDim / 16; ++kk) {
-              const uint32_t off = uint32_t(((kk >> 2) * kBoxBytes + (kk & 3) * 32) >> 4);
-              if (lead) umma_ss(s_tmem, a0 + off, hi, b0 + off, hi, kIdescQK, kk > 0 ? 1u : 0u);
-              PROF_LAP(8 + kk);
-            }
-          }
-#else
           issue_qk(lead, s_tmem, smem_q + q * kTileBytes, k_smem);
           PROF_LAP(5);
-#endif
           if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 4);
           umma_commit_lead(lead, bar(kBarSFull + q));
           if (i + 2 == T) umma_commit_lead(lead, bar(kBarQEmpty + q));
@@ -632,12 +585,7 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
     o_free_parity ^= 1u;
   }
   PROF_LAP(0);
-#ifndef B200ATTN_PROFILE_MMA
   if (lead) PROF_FLUSH(p, 0, 8);
-#endif
-#ifdef B200ATTN_PROFILE_MMA
-  if (lead) { for (int i_ = 0; i_ < 8; ++i_) if (p.trace != nullptr && blockIdx.x == 0) p.trace[24 + 8 * (B200ATTN_PROFILE_MMA - 1) + i_] = prof_acc[i_]; }
-#endif
 
   if (!ok || w.aborted()) {
     // Leaving early: make sure nothing this warp issued is still running before TMEM goes.
@@ -749,12 +697,6 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
     for (int i = 0; i < T; ++i) {
       w.tile = i;
       if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 0);
-#if B200ATTN_S_WAIT_SLEEP_NS > 0
-      // The next scores cannot exist before this tile's PV and the next QK have run (>= ~1000
-      // clocks after P was published): stay off the sub-partition's issue port meanwhile, the
-      // other Q tile's softmax warp lives there too.
-      if (i > 0) __nanosleep(B200ATTN_S_WAIT_SLEEP_NS);
-#endif
       PROF_LAP(0);
       if (!w.wait_warp(bar(kBarSFull + q), s_parity, 300 + q)) return;
       s_parity ^= 1u;
@@ -788,10 +730,6 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
         for (int c = 0; c < kPartAChunks; ++c) {
           exp_chunk(s[c], scale2, neg_m2, packed[c], sum_a, sum_b);
           if (c == 0) tmem_wait_ld();
-#ifdef B200ATTN_TRACE_FINE
-          if (tr && c == 0) B200ATTN_TRACE_EVENT_AFTER(p, q, item, i, 0, 7, __uint_as_float(packed[0][15]));
-          if (tr && c == 1) B200ATTN_TRACE_EVENT_AFTER(p, q, item, i, 0, 0, __uint_as_float(packed[1][15]));
-#endif
         }
         sum_part_a = f2_hsum(sum_a, sum_b);
         // written so that a NaN sum also lands on the exact path
@@ -977,7 +915,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
     ws_softmax_role(p, aux, bar0, tmem_base, warp >> 2, warp & 3, lane, w);
   } else if (warp < 12) {
     reg_shrink<kRegsEpilogue>();
-    w.relaxed = true;
     ws_epilogue_role(p, aux, bar0, tmem_base, warp & 3, lane, w);
   } else {
     reg_shrink<kRegsOther>();
@@ -991,8 +928,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
         tma_prefetch_desc(&tmap_v);
       }
       __syncwarp();
-      w.relaxed = true;
-      ws_load_role(p, &tmap_q, &tmap_k, &tmap_v, smem_q, smem_kv, bar0, lead, w);
+        ws_load_role(p, &tmap_q, &tmap_k, &tmap_v, smem_q, smem_kv, bar0, lead, w);
     }
     __syncwarp();
   }
