@@ -20,6 +20,9 @@ is `batch * N`. Rank 0 prints one JSON line.
                    timed on the same GPU and inputs (null when that library is absent)
 
 `--impl reference` times the CPU arm alone (rank 0 only) and prints the same line shape.
+`--workload dit_1056` times the video-DiT call sequence (528 self- and 528 cross-attention
+launches per step) as one CUDA-graph replay per step, with the eager time beside it;
+`--workload sp_ring` the sequence-parallel K/V ring (needs --gpus >= 2).
 """
 
 from __future__ import annotations
@@ -59,6 +62,13 @@ WORKLOADS = {
 RING_WORKLOADS = {
     "sp_ring": (1, 32, 131072),
     "sp_ring_small": (1, 8, 16384),
+}
+# Video-DiT call sequence: per generation 528 self-attention calls (B, H, L, L) and 528
+# cross-attention calls (B, H, L, Lc), issued back to back on one stream; a step is the whole
+# sequence of 1056 launches (replayed from a CUDA graph, and once eagerly for comparison).
+SEQUENCE_WORKLOADS = {
+    "dit_1056": (1, 12, 32768, 512, 528),
+    "dit_1056_small": (1, 12, 4096, 512, 16),
 }
 
 
@@ -464,6 +474,149 @@ def run_ring(args, rank, local_rank, world):
     dist.destroy_process_group()
 
 
+def video_dit_inputs(torch, b, length, h, seed):
+    """Q/K RMS-normalised per head and scaled by a per-channel N(0,1) gain, V ~ N(0,1): the value
+    distribution of a DiT block after its QK-norm, token-major [B, L, H, 128]."""
+    g = torch.Generator().manual_seed(seed)
+    gain = torch.randn(HEAD_DIM, generator=g)
+    out = []
+    for normed in (True, True, False):
+        x = torch.randn(b, length, h, HEAD_DIM, generator=g)
+        if normed:
+            x = x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + 1e-6) * gain
+        out.append(x.to(torch.bfloat16))
+    return out
+
+
+def run_sequence(args, rank, local_rank, world):
+    """The video-DiT workload: `pairs` x (self-attention, cross-attention) launches per step on one
+    stream, token-major (BSHD) operands used in place. Every rank runs its own replica of the
+    sequence (the calls of one generation are sequentially dependent in the model; replicas stand
+    for independent generations). value = global FLOPs / max-over-ranks time of the graph replay."""
+    import torch
+    import torch.distributed as dist
+
+    from b200_attention_b200 import _native, ops
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    b, h, length, lc, pairs = SEQUENCE_WORKLOADS[args.workload]
+    q_h, k_h, v_h = (t.pin_memory() for t in video_dit_inputs(torch, b, length, h, 77 + rank))
+    _, kc_h, vc_h = (t.pin_memory() for t in video_dit_inputs(torch, b, lc, h, 99 + rank))
+    o_h = torch.empty_like(q_h).pin_memory()
+    q, k, v, kc, vc = (t.to(dev) for t in (q_h, k_h, v_h, kc_h, vc_h))
+    o_self, o_cross = torch.empty_like(q), torch.empty_like(q)
+    stream = torch.cuda.current_stream(dev)
+
+    def sequence():
+        for _ in range(pairs):
+            ops.attention(q, k, v, layout="bshd", out=o_self)
+            ops.attention(q, kc, vc, layout="bshd", out=o_cross)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    steps = args.steps if args.steps_given else 3
+    warmup = max(args.warmup if args.warmup_given else 3, 3)
+    ops.attention(q, k, v, layout="bshd", out=o_self)      # tensor maps cached, device set up
+    ops.attention(q, kc, vc, layout="bshd", out=o_cross)
+    torch.cuda.synchronize(dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        sequence()
+    for _ in range(warmup):
+        graph.replay()
+    barrier()
+    _native.device_check()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(steps):
+        graph.replay()
+    e1.record(stream)
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1)) / steps
+    clocks = sampler.stop() if rank == 0 else None
+    _native.device_check()
+    # the same sequence launched eagerly through the public API, once
+    launches0 = _native.launch_count()
+    barrier()
+    e0.record(stream)
+    sequence()
+    e1.record(stream)
+    barrier()
+    eager_ms = max_over_ranks(e0.elapsed_time(e1))
+    eager_launches = _native.launch_count() - launches0
+    # end to end: operands from pinned host memory in, the last O back out, every step
+    e2e_steps = 2
+    barrier()
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        for d, src in ((q, q_h), (k, k_h), (v, v_h), (kc, kc_h), (vc, vc_h)):
+            d.copy_(src, non_blocking=True)
+        graph.replay()
+        o_h.copy_(o_self, non_blocking=True)
+    e1.record(stream)
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
+    _native.device_check()
+
+    step_flops = pairs * (flops(b, h, length, length) + flops(b, h, length, lc))
+    if rank == 0:
+        peaks = measured_peaks()
+        value = step_flops * world / (ms * 1e-3) / 1e12
+        cpu = None
+        if world == 1 and not args.no_cpu:
+            tf, heads, secs, cores = cpu_sdpa_sample(b, h, length, length, budget_s=args.cpu_budget)
+            cpu = {"value": tf, "unit": "TFLOPS", "cores": cores, "kind": "reference",
+                   "sample": (f"torch scaled_dot_product_attention (math backend, fp32, CPU), {heads} of "
+                              f"{b * h} (batch, head) slices of one self-attention call, {secs:.1f} s, "
+                              "scaled by FLOPs")}
+        in_bytes = (q_h.numel() + k_h.numel() + v_h.numel() + kc_h.numel() + vc_h.numel()) * 2
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": (f"{args.workload}: video-DiT call sequence per GPU, {pairs} x (self-attention "
+                                    f"B={b} H={h} Lq=Lk={length}; cross-attention Lq={length} Lk={lc}), D=128 bf16, "
+                                    "Q/K RMS-normalised per head with N(0,1) gains, V ~ N(0,1), token-major "
+                                    "BSHD in place, one CUDA-graph replay per step"),
+                       "calls_per_step": 2 * pairs, "heads": h, "len_q": length, "len_kv": [length, lc],
+                       "head_dim": HEAD_DIM, "layout": "bshd",
+                       "parallelism": f"independent replicas x{world}, no collective",
+                       "l2_policy": "operands of a self-attention call (288 MiB at L=32768) exceed the 126 MB L2; no flush"},
+            "pct_of_bf16_peak": 100.0 * value / world / peaks["bf16_tflops"],
+            "roofline": {"bound": "tensor", "achieved": value / world, "peak": peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": value / world / peaks["bf16_tflops"],
+                         "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "traffic": None},
+            "eager": {"ms_per_step": eager_ms, "value": step_flops * world / (eager_ms * 1e-3) / 1e12,
+                      "launches": int(eager_launches)},
+            "e2e": {"value": step_flops * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS",
+                    "h2d_bytes_per_step": in_bytes * world, "d2h_bytes_per_step": o_h.numel() * 2 * world,
+                    "ms_per_step": e2e_ms},
+            "gpu_launches": int(2 * pairs * steps), "clocks": clocks, "cpu_baseline": cpu,
+            "k18_same_gpu": None,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def time_k18(torch, q, k, v, layout, args):
     try:
         from oracle import native_refs as R
@@ -497,14 +650,18 @@ def time_k18(torch, q, k, v, layout, args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="main", choices=sorted(WORKLOADS) + sorted(RING_WORKLOADS))
+    ap.add_argument("--workload", default="main",
+                    choices=sorted(WORKLOADS) + sorted(RING_WORKLOADS) + sorted(SEQUENCE_WORKLOADS))
     ap.add_argument("--no-k18", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=12.0)
     args = ap.parse_args()
+    args.steps_given, args.warmup_given = args.steps is not None, args.warmup is not None
+    args.steps = 100 if args.steps is None else args.steps
+    args.warmup = 5 if args.warmup is None else args.warmup
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -517,6 +674,14 @@ def main():
                                   "the reference project has no sequence-parallel path; use --workload main"}))
             return
         run_ring(args, rank, local_rank, world)
+        return
+    if args.workload in SEQUENCE_WORKLOADS:
+        if args.impl == "reference":
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable":
+                                  "the CPU arm times single calls; use --workload dit_self or dit_cross"}))
+            return
+        run_sequence(args, rank, local_rank, world)
         return
     if args.impl == "reference":
         run_reference_arm(args, rank, world)

@@ -156,3 +156,40 @@ def test_host_pipeline_matches_direct_calls(gpu):
         ref = ops.attention(q.cuda(), k.cuda(), v.cuda())
         torch.cuda.synchronize()
         assert torch.equal(o, ref.cpu())
+
+
+def test_calls_can_be_captured_in_a_cuda_graph(gpu):
+    """A sequence of attention calls (self- and cross-attention shapes of a DiT block, token-major
+    in place) is captured once and replayed: launches only, no allocation or synchronisation on
+    the call path once the shapes have been seen. Replays must reproduce the eager results and
+    pick up new operand contents."""
+    from b200_attention_b200 import _native, ops
+
+    dev = torch.device("cuda", 0)
+    q, k, v = (t.to(dev) for t in O.make_inputs_video_dit(4, 1024, 1024, seed=5))
+    _, kc, vc = (t.to(dev) for t in O.make_inputs_video_dit(4, 1024, 384, seed=6))
+    o_self, o_cross = torch.empty_like(q), torch.empty_like(q)
+    ops.attention(q, k, v, layout="bshd", out=o_self)      # first calls set the device up
+    ops.attention(q, kc, vc, layout="bshd", out=o_cross)
+    torch.cuda.synchronize()
+    eager_self, eager_cross = o_self.clone(), o_cross.clone()
+    launches0 = _native.launch_count()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(3):
+            ops.attention(q, k, v, layout="bshd", out=o_self)
+            ops.attention(q, kc, vc, layout="bshd", out=o_cross)
+    assert _native.launch_count() - launches0 == 6
+    o_self.zero_()
+    o_cross.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    _native.device_check()
+    assert torch.equal(o_self, eager_self) and torch.equal(o_cross, eager_cross)
+    # new contents in the same buffers are picked up by a replay
+    q.copy_(q.flip(1))
+    graph.replay()
+    torch.cuda.synchronize()
+    _native.device_check()
+    ref, _ = O.sdpa_explicit(O.to_bhld(q.cpu()), O.to_bhld(k.cpu()), O.to_bhld(v.cpu()))
+    O.assert_within_contract(O.compare(O.to_bhld(o_self.cpu()), ref))
