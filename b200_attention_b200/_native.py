@@ -83,6 +83,8 @@ class ForwardArgs(C.Structure):
         ("partial_merge", C.c_int32),
         ("partial_emit", C.c_int32),
         ("stream", C.c_void_p),
+        ("causal", C.c_int32),
+        ("heads_kv", C.c_int32),
     ]
 
 

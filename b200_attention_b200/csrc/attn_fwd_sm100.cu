@@ -380,13 +380,28 @@ struct ItemCoord {
   int b, h, row0;
 };
 
+// Work items are numbered (batch, head)-major, so consecutive items share K/V in L2. With a causal
+// mask the query blocks of a head are walked from the last (longest) to the first, so the
+// round-robin assignment hands every CTA a mix of long and short items.
+template <bool kCausal>
 __device__ __forceinline__ ItemCoord decode_item(const FwdParams& p, int item) {
   ItemCoord c;
   const int bh = item / p.m_blocks;
-  c.row0 = (item - bh * p.m_blocks) * kItemRows;
+  const int mb = item - bh * p.m_blocks;
+  c.row0 = (kCausal ? p.m_blocks - 1 - mb : mb) * kItemRows;
   c.b = bh / p.heads;
   c.h = bh - c.b * p.heads;
   return c;
+}
+
+// K/V tiles an item visits: all of them, or with a causal mask (key j is visible to row i iff
+// j <= i + causal_off, causal_off = len_kv - len_q >= 0) those up to its last row's diagonal.
+template <bool kCausal>
+__device__ __forceinline__ int item_tiles(const FwdParams& p, int row0) {
+  if (!kCausal) return p.kv_tiles;
+  const int last_row = min(row0 + kItemRows, p.len_q) - 1;
+  const int tiles = (last_row + p.causal_off + kBlockN) / kBlockN;  // ceil((last_row + off + 1) / 128)
+  return min(p.kv_tiles, tiles);
 }
 
 // ---- TMA producer -------------------------------------------------------------------------
@@ -397,6 +412,7 @@ __device__ __forceinline__ void load_tile(uint32_t lead, uint32_t dst, const CUt
   tma_load_4d_lead(lead, dst + kBoxBytes, map, 64, row, h, b, bar);
 }
 
+template <bool kCausal>
 __device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CUtensorMap* tk,
                              const CUtensorMap* tv, uint32_t smem_q, uint32_t smem_kv,
                              uint32_t bar0, uint32_t lead, WaitCtx& w) {
@@ -437,14 +453,17 @@ __device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CU
     return true;
   };
 
-  const int T = p.kv_tiles;
   bool first = true;
   for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
-    const ItemCoord c = decode_item(p, item);
+    const ItemCoord c = decode_item<kCausal>(p, item);
+    const int T = item_tiles<kCausal>(p, c.row0);
+    // K/V coordinates: grouped-query attention maps kv_group query heads onto one K/V head
+    ItemCoord kvc = c;
+    kvc.h = c.h / p.kv_group;
     w.item = item;
     w.tile = 0;
     if (first) {
-      ok = push_pair(false, 0, c, true, 0, c, 110);  // K_0 of the first item travels alone
+      ok = push_pair(false, 0, kvc, true, 0, kvc, 110);  // K_0 of the first item travels alone
       first = false;
       if (!ok) break;
     }
@@ -461,13 +480,17 @@ __device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CU
     for (int i = 0; ok && i < T; ++i) {
       w.tile = i;
       if (i + 1 < T) {
-        ok = push_pair(true, i * kBlockN, c, true, (i + 1) * kBlockN, c, 111);
+        ok = push_pair(true, i * kBlockN, kvc, true, (i + 1) * kBlockN, kvc, 111);
       } else {
         // the last V of this item shares its pair with K_0 of the CTA's next item, if any
         const int next_item = item + int(gridDim.x);
         const bool has_next_item = next_item < p.total_items;
-        ok = push_pair(true, i * kBlockN, c, has_next_item, 0,
-                       has_next_item ? decode_item(p, next_item) : c, 112);
+        ItemCoord next_kvc = kvc;
+        if (has_next_item) {
+          next_kvc = decode_item<kCausal>(p, next_item);
+          next_kvc.h /= p.kv_group;
+        }
+        ok = push_pair(true, i * kBlockN, kvc, has_next_item, 0, next_kvc, 112);
       }
     }
   }
@@ -488,6 +511,7 @@ __device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CU
 }
 
 // ---- MMA issuer ---------------------------------------------------------------------------
+template <bool kCausal>
 __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_kv, uint32_t bar0,
                             uint32_t tmem_base, uint32_t lead, WaitCtx& w) {
   // Run by the whole warp with uniform control flow; `lead` marks the one lane that issues.
@@ -502,10 +526,10 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
   // an item has already arrived with the last V of the item before.
   bool k_ready = false;
 
-  const int T = p.kv_tiles;
   PROF_DECL(8);  // 0 other, 1 wait pair, 3 wait P (+O_FREE), 4 issue PV, 5 issue QK, 6 commits
 
   for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
+    const int T = kCausal ? item_tiles<true>(p, decode_item<true>(p, item).row0) : p.kv_tiles;
     w.item = item;
     w.tile = 0;
     // ---- tile 0 scores for both Q tiles
@@ -659,6 +683,7 @@ __device__ __forceinline__ float f2_hsum(f2 a, f2 b) {
 // exist, so the previous PV has finished, and the next PV has not been released yet), and redo
 // part A. Nothing is published before the decision, so there is never anything to retract.
 // Part A is handed to the MMA warp first so its PV steps overlap the work on part B.
+template <bool kCausal>
 __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, uint32_t tmem_base,
                                 int q, int warp_in_group, int lane, WaitCtx& w) {
   auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
@@ -671,8 +696,8 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
   const int r = warp_in_group * 32 + lane;
   const float scale_log2 = p.scale_log2;
   const f2 scale2 = f2_splat(scale_log2);
-  const int T = p.kv_tiles;
-  const int tail_valid = p.len_kv - (T - 1) * kBlockN;  // keys in the last tile, 1..128
+  const int last_tile = p.kv_tiles - 1;
+  const int tail_valid = p.len_kv - last_tile * kBlockN;  // keys in the last tile, 1..128
 #ifdef B200ATTN_TRACE
   const bool tr = (warp_in_group == B200ATTN_TRACE_WARP && lane == 0);
 #else
@@ -694,6 +719,11 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
     fin_free_parity ^= 1u;
     float m = kNegInf;  // reference maximum, log2 units
     float l = 0.0f;     // running sum of 2^(s - m)
+    // causal: this row sees keys 0 .. row + causal_off; its Q tile's first row sees the fewest
+    const int row0 = kCausal ? decode_item<true>(p, item).row0 : 0;
+    const int T = item_tiles<kCausal>(p, row0);
+    const int tile_limit = row0 + q * kBlockM + p.causal_off;  // last key the tile's first row sees
+    const int row_limit = tile_limit + r;                      // last key this row sees
     for (int i = 0; i < T; ++i) {
       w.tile = i;
       if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 0);
@@ -712,9 +742,16 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
       tmem_ld32(s_tmem + 96, s[3]);
       PROF_LAP(2);
       if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 2);
-      const bool tail = (i == T - 1 && tail_valid < kBlockN);
+      // keys of this tile that exist for this row: all 128, fewer in a ragged last tile, and with
+      // a causal mask fewer (possibly none) in the tiles the diagonal crosses
+      bool tail = (i == last_tile && tail_valid < kBlockN);
+      int valid = tail ? tail_valid : kBlockN;
+      if (kCausal && i * kBlockN + kBlockN - 1 > tile_limit) {
+        tail = true;
+        valid = min(valid, row_limit - i * kBlockN + 1);
+      }
       if (tail || i == 0 || kPartAChunks < 4) tmem_wait_ld();  // these paths look at all chunks at once
-      if (tail) mask_tail(s, tail_valid);
+      if (tail) mask_tail(s, valid);
 
       uint32_t packed[kPartAChunks][16];
       f2 sum_a = f2_splat(0.0f), sum_b = f2_splat(0.0f);
@@ -744,7 +781,7 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
 #pragma unroll
           for (int c = 0; c < kPartAChunks; ++c) tmem_ld32(s_tmem + c * 32, s[c]);
           tmem_wait_ld();
-          if (tail) mask_tail(s, tail_valid);
+          if (tail) mask_tail(s, valid);
         }
         const float tile_max = row_max(s) * scale_log2;
         if (i == 0) {
@@ -821,6 +858,7 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
 // ---- epilogue -------------------------------------------------------------------------------
 // Once per item and Q tile: take the final (max, sum) from the softmax group, read the
 // accumulator out of TMEM, normalise, optionally merge with a stored partial, store O / LSE.
+template <bool kCausal>
 __device__ void ws_epilogue_role(const FwdParams& p, WsAux* aux, uint32_t bar0, uint32_t tmem_base,
                                  int warp_in_group, int lane, WaitCtx& w) {
   auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
@@ -831,7 +869,7 @@ __device__ void ws_epilogue_role(const FwdParams& p, WsAux* aux, uint32_t bar0, 
   for (int item = blockIdx.x; item < p.total_items; item += gridDim.x) {
     w.item = item;
     w.tile = p.kv_tiles;
-    const ItemCoord c = decode_item(p, item);
+    const ItemCoord c = decode_item<kCausal>(p, item);
     for (int q = 0; q < kQTilesPerItem; ++q) {
       if (!w.wait_warp(bar(kBarFin + q), fin_parity, 410 + q)) return;
       if (!w.wait_warp(bar(kBarPvDone + q), fin_parity, 420 + q)) return;
@@ -853,6 +891,7 @@ __device__ void ws_epilogue_role(const FwdParams& p, WsAux* aux, uint32_t bar0, 
   }
 }
 
+template <bool kCausal>
 __global__ void __launch_bounds__(kWsThreads, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
                    const __grid_constant__ CUtensorMap tmap_k,
@@ -912,15 +951,15 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
   if (warp < 8) {
     reg_grow<kRegsSoftmax>();
-    ws_softmax_role(p, aux, bar0, tmem_base, warp >> 2, warp & 3, lane, w);
+    ws_softmax_role<kCausal>(p, aux, bar0, tmem_base, warp >> 2, warp & 3, lane, w);
   } else if (warp < 12) {
     reg_shrink<kRegsEpilogue>();
-    ws_epilogue_role(p, aux, bar0, tmem_base, warp & 3, lane, w);
+    ws_epilogue_role<kCausal>(p, aux, bar0, tmem_base, warp & 3, lane, w);
   } else {
     reg_shrink<kRegsOther>();
     const uint32_t lead = (lane == 0) ? 1u : 0u;
     if (warp == 12) {
-      ws_mma_role(p, smem_q, smem_kv, bar0, tmem_base, lead, w);
+      ws_mma_role<kCausal>(p, smem_q, smem_kv, bar0, tmem_base, lead, w);
     } else if (warp == 13) {
       if (lead) {
         tma_prefetch_desc(&tmap_q);
@@ -928,7 +967,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
         tma_prefetch_desc(&tmap_v);
       }
       __syncwarp();
-        ws_load_role(p, &tmap_q, &tmap_k, &tmap_v, smem_q, smem_kv, bar0, lead, w);
+        ws_load_role<kCausal>(p, &tmap_q, &tmap_k, &tmap_v, smem_q, smem_kv, bar0, lead, w);
     }
     __syncwarp();
   }
@@ -1123,14 +1162,17 @@ cudaError_t prepare_kernels() {
   // The warp-specialised kernel re-partitions registers between its roles. A growing role
   // blocks in hardware until the CTA's pool has room, so refuse to run unless the pool the
   // launch reserves (registers per thread x 512 threads) covers what the roles ask for.
-  cudaFuncAttributes fa;
-  cudaError_t e = cudaFuncGetAttributes(&fa, attn_fwd_ws_kernel);
-  if (e != cudaSuccess) return e;
   constexpr int kPoolNeeded = 128 * (2 * kRegsSoftmax + kRegsEpilogue + kRegsOther);
-  if (fa.numRegs * kWsThreads < kPoolNeeded) return cudaErrorLaunchOutOfResources;
-  e = cudaFuncSetAttribute(attn_fwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           kWsSmemBytes);
-  if (e != cudaSuccess) return e;
+  const void* ws_kernels[2] = {reinterpret_cast<const void*>(&attn_fwd_ws_kernel<false>),
+                               reinterpret_cast<const void*>(&attn_fwd_ws_kernel<true>)};
+  for (const void* kernel : ws_kernels) {
+    cudaFuncAttributes fa;
+    cudaError_t e = cudaFuncGetAttributes(&fa, kernel);
+    if (e != cudaSuccess) return e;
+    if (fa.numRegs * kWsThreads < kPoolNeeded) return cudaErrorLaunchOutOfResources;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsSmemBytes);
+    if (e != cudaSuccess) return e;
+  }
   return cudaFuncSetAttribute(attn_fwd_serial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               kSerialSmemBytes);
 }
@@ -1138,7 +1180,11 @@ cudaError_t prepare_kernels() {
 cudaError_t launch_fwd_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                           const FwdParams& p, int sm_count, cudaStream_t stream) {
   const int grid = p.total_items < sm_count ? p.total_items : sm_count;
-  attn_fwd_ws_kernel<<<grid, kWsThreads, kWsSmemBytes, stream>>>(tq, tk, tv, p);
+  if (p.causal) {
+    attn_fwd_ws_kernel<true><<<grid, kWsThreads, kWsSmemBytes, stream>>>(tq, tk, tv, p);
+  } else {
+    attn_fwd_ws_kernel<false><<<grid, kWsThreads, kWsSmemBytes, stream>>>(tq, tk, tv, p);
+  }
   return cudaGetLastError();
 }
 

@@ -45,6 +45,9 @@ struct FwdParams {
   int32_t m_blocks;     // ceil(len_q / kItemRows)
   int32_t kv_tiles;     // ceil(len_kv / kBlockN)
   int32_t total_items;  // batch * heads * m_blocks
+  int32_t kv_group;     // query heads per K/V head (1 unless grouped-query attention)
+  int32_t causal;       // 1: key j is visible to row i iff j <= i + causal_off
+  int32_t causal_off;   // len_kv - len_q (>= 0): the mask is aligned to the bottom-right corner
   float scale_log2;     // softmax_scale * log2(e)
   int32_t* status;      // kStatusInts ints the kernel can write (device or mapped host memory)
   uint32_t wait_limit_ms;

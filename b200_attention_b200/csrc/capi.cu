@@ -230,10 +230,18 @@ int b200attn_forward(const b200attn_forward_args* a) {
     return fail(B200ATTN_ERR_INVALID_ARGUMENT, "unknown kernel selector");
   if (int64_t(a->batch) * a->heads > 65535 * 16)
     return fail(B200ATTN_ERR_UNSUPPORTED, "batch * heads too large");
+  const int heads_kv = a->heads_kv > 0 ? a->heads_kv : a->heads;
+  if (a->heads_kv < 0 || a->heads % heads_kv != 0)
+    return fail(B200ATTN_ERR_INVALID_ARGUMENT, "heads must be a positive multiple of heads_kv");
+  if (a->causal != 0 && a->len_kv < a->len_q)
+    return fail(B200ATTN_ERR_UNSUPPORTED,
+                "causal attention needs len_kv >= len_q (the mask is aligned to the bottom-right corner)");
+  if ((a->causal != 0 || heads_kv != a->heads) && a->kernel != B200ATTN_KERNEL_WARP_SPECIALIZED)
+    return fail(B200ATTN_ERR_UNSUPPORTED, "causal masks and grouped K/V heads need the warp-specialised kernel");
   int rc;
   if ((rc = check_operand("q", a->q, a->batch, a->heads, a->len_q)) != 0) return rc;
-  if ((rc = check_operand("k", a->k, a->batch, a->heads, a->len_kv)) != 0) return rc;
-  if ((rc = check_operand("v", a->v, a->batch, a->heads, a->len_kv)) != 0) return rc;
+  if ((rc = check_operand("k", a->k, a->batch, heads_kv, a->len_kv)) != 0) return rc;
+  if ((rc = check_operand("v", a->v, a->batch, heads_kv, a->len_kv)) != 0) return rc;
   if ((rc = check_operand("o", a->o, a->batch, a->heads, a->len_q)) != 0) return rc;
   if ((a->partial_merge != 0 || a->partial_emit != 0) &&
       (a->partial_o == nullptr || a->partial_lse == nullptr))
@@ -265,6 +273,9 @@ int b200attn_forward(const b200attn_forward_args* a) {
   if (items >= (int64_t(1) << 30) || serial_ctas >= (int64_t(1) << 30))
     return fail(B200ATTN_ERR_UNSUPPORTED, "too many work items");
   p.total_items = int32_t(items);
+  p.kv_group = a->heads / heads_kv;
+  p.causal = a->causal != 0;
+  p.causal_off = a->len_kv - a->len_q;
   const float scale = a->softmax_scale > 0.0f ? a->softmax_scale : 1.0f / std::sqrt(float(kHeadDim));
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = st->status_dev;
@@ -279,8 +290,8 @@ int b200attn_forward(const b200attn_forward_args* a) {
 
   CUtensorMap tq, tk, tv;
   const MapKey kq{a->q.ptr, a->q.stride_batch, a->q.stride_head, a->q.stride_row, a->batch, a->heads, a->len_q, device};
-  const MapKey kk{a->k.ptr, a->k.stride_batch, a->k.stride_head, a->k.stride_row, a->batch, a->heads, a->len_kv, device};
-  const MapKey kv{a->v.ptr, a->v.stride_batch, a->v.stride_head, a->v.stride_row, a->batch, a->heads, a->len_kv, device};
+  const MapKey kk{a->k.ptr, a->k.stride_batch, a->k.stride_head, a->k.stride_row, a->batch, heads_kv, a->len_kv, device};
+  const MapKey kv{a->v.ptr, a->v.stride_batch, a->v.stride_head, a->v.stride_row, a->batch, heads_kv, a->len_kv, device};
   if ((rc = make_tensor_map(kq, &tq)) != 0) return rc;
   if ((rc = make_tensor_map(kk, &tk)) != 0) return rc;
   if ((rc = make_tensor_map(kv, &tv)) != 0) return rc;

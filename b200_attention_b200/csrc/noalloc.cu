@@ -108,6 +108,8 @@ extern "C" B200ATTN_API int b200attn_forward_kv_split_noalloc(const b200attn_for
     return fail(B200ATTN_ERR_INVALID_ARGUMENT, "the no-allocation entry point runs the warp-specialised kernel only");
   if (a->partial_o != nullptr || a->partial_lse != nullptr || a->partial_merge != 0 || a->partial_emit != 0)
     return fail(B200ATTN_ERR_INVALID_ARGUMENT, "partial_* must be unset: the partial state lives in the built-in scratch");
+  if (a->causal != 0 || (a->heads_kv != 0 && a->heads_kv != a->heads))
+    return fail(B200ATTN_ERR_UNSUPPORTED, "the no-allocation entry point has no causal mask and no grouped K/V heads");
   const int64_t rows = int64_t(a->batch) * a->heads * a->len_q;
   if (rows > kMaxRows) {
     char buf[200];
@@ -177,6 +179,7 @@ extern "C" B200ATTN_API int b200attn_forward_kv_split_noalloc(const b200attn_for
   p.len_q = a->len_q;
   p.m_blocks = (a->len_q + kItemRows - 1) / kItemRows;
   p.total_items = int32_t(int64_t(a->batch) * a->heads * p.m_blocks);
+  p.kv_group = 1;
   const float scale = a->softmax_scale > 0.0f ? a->softmax_scale : 1.0f / std::sqrt(float(kHeadDim));
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;

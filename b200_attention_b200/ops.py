@@ -41,6 +41,7 @@ def attention(
     *,
     layout: str = "bhld",
     softmax_scale: float = 0.0,
+    causal: bool = False,
     return_lse: bool = False,
     out: Optional[torch.Tensor] = None,
     kernel: int = N.KERNEL_WARP_SPECIALIZED,
@@ -53,6 +54,9 @@ def attention(
 
     q: [B, H, Lq, 128] ('bhld') or [B, Lq, H, 128] ('bshd'), bf16, CUDA; k, v likewise with Lk.
     Returns O (same layout as q) and, if asked, LSE [B, H, Lq] fp32 (natural log).
+    k and v may have fewer heads than q (grouped-query attention: query head h reads K/V head
+    h // (H // Hkv)). `causal=True` masks key j for query row i unless j <= i + (Lk - Lq)
+    (bottom-right aligned, needs Lk >= Lq).
     `partial=(o_fp32 [B,H,Lq,128], lse_fp32 [B,H,Lq])` with the two flags chains calls over K/V
     shards; see include/b200_attention.h.
     """
@@ -71,8 +75,10 @@ def attention(
         raise RuntimeError("q, k, v must be on the same device")
     B, H, Lq = _dims(q, layout)
     Bk, Hk, Lk = _dims(k, layout)
-    if (Bk, Hk) != (B, H) or tuple(k.shape) != tuple(v.shape):
-        raise RuntimeError("q, k, v disagree on batch / heads, or k and v differ in shape")
+    if Bk != B or tuple(k.shape) != tuple(v.shape):
+        raise RuntimeError("q, k, v disagree on batch, or k and v differ in shape")
+    if Hk < 1 or H % Hk != 0:
+        raise RuntimeError(f"q has {H} heads, k and v have {Hk}: not a whole number of query heads per K/V head")
 
     with torch.cuda.device(q.device):
         if out is None:
@@ -88,6 +94,8 @@ def attention(
         a.lse = lse.data_ptr() if lse is not None else None
         a.softmax_scale = float(softmax_scale)
         a.kernel = int(kernel)
+        a.causal = int(bool(causal))
+        a.heads_kv = Hk
         if partial is not None:
             po, pl = partial
             if po.dtype != torch.float32 or pl.dtype != torch.float32 or not po.is_contiguous() \

@@ -81,6 +81,17 @@ typedef struct b200attn_forward_args {
   int32_t partial_merge;
   int32_t partial_emit;
   void* stream; /* cudaStream_t; NULL = the legacy default stream */
+  /* Causal mask and grouped-query attention (warp-specialised kernel only). The reference's
+   * shipped kernels are dense and ungrouped; its research kernel
+   * (research/causal_gqa_2cta.cu:1131-1137: always causal, square, heads == 4 * heads_kv, BSHD)
+   * is the adjacent operator these two fields cover.
+   *   causal   != 0: key j is visible to query row i iff j <= i + (len_kv - len_q), i.e. the mask
+   *                  is aligned to the bottom-right corner; needs len_kv >= len_q.
+   *   heads_kv  > 0: k and v have heads_kv heads (their strides and extents refer to that many);
+   *                  query head h reads K/V head h / (heads / heads_kv); heads % heads_kv == 0.
+   *                  0 means heads_kv == heads. */
+  int32_t causal;
+  int32_t heads_kv;
 } b200attn_forward_args;
 
 /* Asynchronous on args->stream. The device that is current when the call is made is used. */

@@ -1,7 +1,8 @@
 """Generates tests/golden/*.npz by running the reference project's own oracle call
 (torch scaled_dot_product_attention, math backend, fp32, CPU: benchmarks/check_correctness.py:89-95
 and capstone-project/tests/test_kernel.py:121-130) on seeded inputs drawn with the reference's
-seeding protocols. LSE comes from torch.logsumexp over the fp32 scores.
+seeding protocols. LSE comes from torch.logsumexp over the fp32 scores. The causal_* files come from the same call
+with `is_causal=True` (and `enable_gqa=True`) on square cases.
 
     python tests/golden/make_golden.py
 
@@ -38,6 +39,22 @@ CASES = {
 }
 
 
+# Causal mask and grouped K/V heads (the reference's research operator, research/causal_gqa_2cta.cu):
+# name -> (benchmark-generator kwargs, K/V heads). Square, so PyTorch's `is_causal` applies as is;
+# K and V keep every (heads // heads_kv)-th head of the drawn tensors.
+CAUSAL_CASES = {
+    "causal_b1_h4_kv1_l384": (dict(batch=1, heads=4, len_q=384, len_kv=384, seed=11), 1),
+    "causal_b2_h4_kv2_l256": (dict(batch=2, heads=4, len_q=256, len_kv=256, seed=12), 2),
+}
+
+
+def draw_causal(kwargs: dict, heads_kv: int):
+    """q [B,H,L,128], k and v [B,Hkv,L,128], bf16 CPU."""
+    q, k, v = (O.to_bhld(t) for t in O.make_inputs_benchmark(**kwargs))
+    step = kwargs["heads"] // heads_kv
+    return q, k[:, ::step].contiguous(), v[:, ::step].contiguous()
+
+
 def draw(generator: str, kwargs: dict):
     """Returns q, k, v as BHLD bf16 CPU tensors."""
     if generator == "benchmark":
@@ -71,6 +88,21 @@ def main() -> None:
             HERE / f"{name}.npz",
             generator=generator,
             kwargs=repr(kwargs),
+            input_sha256=input_digest(q, k, v),
+            o=o.numpy().astype(np.float32),
+            lse=lse.numpy().astype(np.float32),
+            torch_version=torch.__version__,
+        )
+        print(name, tuple(o.shape), input_digest(q, k, v)[:12])
+    for name, (kwargs, heads_kv) in CAUSAL_CASES.items():
+        q, k, v = draw_causal(kwargs, heads_kv)
+        o = O.sdpa_torch_math(q, k, v, causal=True)
+        _, lse = O.sdpa_explicit(q, k, v, causal=True)
+        np.savez_compressed(
+            HERE / f"{name}.npz",
+            generator="benchmark",
+            kwargs=repr(kwargs),
+            heads_kv=heads_kv,
             input_sha256=input_digest(q, k, v),
             o=o.numpy().astype(np.float32),
             lse=lse.numpy().astype(np.float32),

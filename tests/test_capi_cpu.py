@@ -38,9 +38,10 @@ def test_version_and_status_strings(native_built):
 
 
 def test_struct_layout_matches_header(native_built):
-    # 6 x 4 bytes, 4 operands of 32 bytes, lse ptr, scale + kernel, 2 ptrs, 2 ints, stream
+    # 6 x 4 bytes, 4 operands of 32 bytes, lse ptr, scale + kernel, 2 ptrs, 2 ints, stream,
+    # causal + heads_kv
     assert C.sizeof(N.Operand) == 32
-    assert C.sizeof(N.ForwardArgs) == 24 + 4 * 32 + 8 + 8 + 16 + 8 + 8
+    assert C.sizeof(N.ForwardArgs) == 24 + 4 * 32 + 8 + 8 + 16 + 8 + 8 + 8
 
 
 def _args(**over):
@@ -66,6 +67,11 @@ def _args(**over):
     (dict(o=N.Operand(0x10000, 0, 256 * 128, 64)), N.STATUS_INVALID_ARGUMENT),   # stride < 128
     (dict(partial_merge=1), N.STATUS_INVALID_ARGUMENT),                          # no scratch given
     (dict(softmax_scale=float("nan")), N.STATUS_INVALID_ARGUMENT),
+    (dict(heads=4, heads_kv=3), N.STATUS_INVALID_ARGUMENT),                      # 4 % 3 != 0
+    (dict(heads_kv=-1), N.STATUS_INVALID_ARGUMENT),
+    (dict(causal=1, len_q=512), N.STATUS_UNSUPPORTED),                           # len_kv < len_q
+    (dict(causal=1, kernel=1), N.STATUS_UNSUPPORTED),                            # serial kernel
+    (dict(heads=4, heads_kv=2, kernel=1), N.STATUS_UNSUPPORTED),
 ])
 def test_argument_errors_come_back_as_status_codes(native_built, over, status):
     a = _args(**over)
