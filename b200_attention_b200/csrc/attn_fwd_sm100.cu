@@ -381,14 +381,28 @@ struct ItemCoord {
 };
 
 // Work items are numbered (batch, head)-major, so consecutive items share K/V in L2. With a causal
-// mask the query blocks of a head are walked from the last (longest) to the first, so the
-// round-robin assignment hands every CTA a mix of long and short items.
+// mask items differ in length (2 .. 2 * m_blocks tiles), so they are dealt longest first: heads are
+// taken in groups of kCausalHeadGroup (K/V of a group, and of the next one starting, fit in L2),
+// and inside a group the query block index falls slowest and the head changes fastest, so the
+// round-robin assignment hands every CTA nearly the same multiset of lengths.
+constexpr int kCausalHeadGroup = 8;
 template <bool kCausal>
 __device__ __forceinline__ ItemCoord decode_item(const FwdParams& p, int item) {
   ItemCoord c;
-  const int bh = item / p.m_blocks;
-  const int mb = item - bh * p.m_blocks;
-  c.row0 = (kCausal ? p.m_blocks - 1 - mb : mb) * kItemRows;
+  int bh, mb;
+  if (kCausal) {
+    const int per_group = kCausalHeadGroup * p.m_blocks;
+    const int group = item / per_group;
+    const int idx = item - group * per_group;
+    const int heads_here = min(kCausalHeadGroup, p.batch * p.heads - group * kCausalHeadGroup);
+    const int mb_rev = idx / heads_here;
+    bh = group * kCausalHeadGroup + (idx - mb_rev * heads_here);
+    mb = p.m_blocks - 1 - mb_rev;
+  } else {
+    bh = item / p.m_blocks;
+    mb = item - bh * p.m_blocks;
+  }
+  c.row0 = mb * kItemRows;
   c.b = bh / p.heads;
   c.h = bh - c.b * p.heads;
   return c;

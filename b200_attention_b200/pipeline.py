@@ -15,11 +15,12 @@ from . import ops
 
 class HostPipeline:
     def __init__(self, shape_q: Tuple[int, ...], shape_kv: Tuple[int, ...], *, layout: str = "bhld",
-                 device=None, depth: int = 2, softmax_scale: float = 0.0):
+                 device=None, depth: int = 2, softmax_scale: float = 0.0, causal: bool = False):
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.layout = layout
         self.depth = depth
         self.scale = softmax_scale
+        self.causal = causal
         mk = lambda shape: torch.empty(shape, dtype=torch.bfloat16, device=self.device)
         self.slots = [dict(q=mk(shape_q), k=mk(shape_kv), v=mk(shape_kv), o=mk(shape_q)) for _ in range(depth)]
         self.s_in = torch.cuda.Stream(self.device)
@@ -48,7 +49,7 @@ class HostPipeline:
             if reused:
                 self.s_run.wait_event(self.ev_out[s])  # the previous result left this slot
             ops.attention(slot["q"], slot["k"], slot["v"], layout=self.layout, out=slot["o"],
-                          softmax_scale=self.scale, stream=self.s_run)
+                          softmax_scale=self.scale, causal=self.causal, stream=self.s_run)
             self.ev_run[s].record(self.s_run)
         with torch.cuda.stream(self.s_out):
             self.s_out.wait_event(self.ev_run[s])

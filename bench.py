@@ -56,6 +56,13 @@ WORKLOADS = {
     "dit_self": (1, 12, 32768, 32768, "bshd"),
     "dit_cross": (1, 12, 32768, 512, "bshd"),
     "smoke": (1, 4, 1024, 1024, "bhld"),
+    "causal": (4, 16, 8192, 8192, "bhld"),        # the headline shape with a causal mask
+    "causal_gqa": (4, 16, 8192, 8192, "bshd"),    # causal, 4 query heads per K/V head, token-major
+}
+# Variants of the operator: causal mask (bottom-right aligned) and K/V heads (grouped-query).
+WORKLOAD_OPTIONS = {
+    "causal": {"causal": True},
+    "causal_gqa": {"causal": True, "heads_kv": 4},
 }
 # Sequence-parallel long-context workload: the GLOBAL problem (batch, heads, len) is fixed and
 # split by query rows / key rows over the ranks (strong scaling; needs --gpus >= 2 to be a ring).
@@ -77,8 +84,10 @@ SEQUENCE_WORKLOADS = {
 NCU_TRAFFIC_BYTES = {"main": 515.5e6}
 
 
-def flops(b, h, lq, lk):
-    return 4.0 * b * h * lq * lk * HEAD_DIM
+def flops(b, h, lq, lk, causal=False):
+    """4 * B * H * D * (query, key) pairs; with a causal mask only the visible pairs count."""
+    pairs = lq * lk if not causal else lq * (lq + 1) // 2 + (lk - lq) * lq
+    return 4.0 * b * h * pairs * HEAD_DIM
 
 
 def measured_peaks():
@@ -170,7 +179,7 @@ def physical_gpu_index(local_rank: int) -> int:
 # --------------------------------------------------------------------------------------------
 # CPU arm: the reference project's own check call, torch SDPA math backend in fp32
 # --------------------------------------------------------------------------------------------
-def cpu_sdpa_sample(b, h, lq, lk, budget_s: float, max_heads: int | None = None):
+def cpu_sdpa_sample(b, h, lq, lk, budget_s: float, max_heads: int | None = None, causal: bool = False):
     """Times torch SDPA (math, fp32, CPU) head by head on inputs of the workload's distribution
     until `budget_s` is spent. Returns (tflops, heads_done, seconds, cores)."""
     import torch
@@ -194,29 +203,33 @@ def cpu_sdpa_sample(b, h, lq, lk, budget_s: float, max_heads: int | None = None)
     k = torch.randn(1, 1, lk, HEAD_DIM, generator=g).to(torch.bfloat16)
     v = torch.randn(1, 1, lk, HEAD_DIM, generator=g).to(torch.bfloat16)
     O.sdpa_torch_math(q[:, :, :64], k, v)  # warm the thread pool
+    # the causal form of the call applies to whole square problems only; otherwise the dense call
+    # is timed and credited with the dense FLOPs
+    causal = causal and rows == lq == lk
     while heads < total and t_total < budget_s:
         t0 = time.perf_counter()
         for r0 in range(0, lq, rows):
-            O.sdpa_torch_math(q[:, :, : min(rows, lq - r0)], k, v)
+            O.sdpa_torch_math(q[:, :, : min(rows, lq - r0)], k, v, causal=causal)
             if time.perf_counter() - t0 + t_total > 3 * budget_s:
                 break
         dt = time.perf_counter() - t0
         t_total += dt
-        done_flops += flops(1, 1, lq, lk)
+        done_flops += flops(1, 1, lq, lk, causal)
         heads += 1
     return done_flops / t_total / 1e12, heads, t_total, cores
 
 
 def run_reference_arm(args, rank, world):
     b, h, lq, lk, layout = WORKLOADS[args.workload]
+    causal = bool(WORKLOAD_OPTIONS.get(args.workload, {}).get("causal", False))
     if rank != 0:
         return
     per_step_budget = max(1.0, min(20.0, 90.0 / max(args.steps + args.warmup, 1)))
     for _ in range(args.warmup):
-        cpu_sdpa_sample(b, h, lq, lk, budget_s=per_step_budget / 4, max_heads=1)
+        cpu_sdpa_sample(b, h, lq, lk, budget_s=per_step_budget / 4, max_heads=1, causal=causal)
     vals, heads_done, secs, cores = [], 0, 0.0, 0
     for _ in range(args.steps):
-        tf, heads, t, cores = cpu_sdpa_sample(b, h, lq, lk, budget_s=per_step_budget)
+        tf, heads, t, cores = cpu_sdpa_sample(b, h, lq, lk, budget_s=per_step_budget, causal=causal)
         vals.append(tf)
         heads_done += heads
         secs += t
@@ -226,7 +239,7 @@ def run_reference_arm(args, rank, world):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": flops(b * world, h, lq, lk) / (value * 1e12) * 1e3,
+        "ms_per_step": flops(b * world, h, lq, lk, causal) / (value * 1e12) * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32",
         "data": "synthetic", "config": workload_config(args.workload, world),
         "cpu_baseline": {"value": value, "unit": "TFLOPS", "cores": cores, "kind": "reference",
@@ -239,9 +252,13 @@ def run_reference_arm(args, rank, world):
 
 def workload_config(name, world):
     b, h, lq, lk, layout = WORKLOADS[name]
-    return {"workload": f"{name}: dense non-causal attention forward, B={b} per GPU, H={h}, Lq={lq}, "
+    opts = WORKLOAD_OPTIONS.get(name, {})
+    kind = "causal (bottom-right aligned)" if opts.get("causal") else "non-causal"
+    kv = f", {opts['heads_kv']} K/V heads" if "heads_kv" in opts else ""
+    return {"workload": f"{name}: dense {kind} attention forward, B={b} per GPU, H={h}{kv}, Lq={lq}, "
                         f"Lk={lk}, D=128, bf16 N(0,1), scale 1/sqrt(128), layout {layout.upper()}",
-            "global_batch": b * world, "heads": h, "len_q": lq, "len_kv": lk, "head_dim": HEAD_DIM,
+            "global_batch": b * world, "heads": h, "heads_kv": opts.get("heads_kv", h),
+            "causal": bool(opts.get("causal", False)), "len_q": lq, "len_kv": lk, "head_dim": HEAD_DIM,
             "layout": layout, "parallelism": f"(batch,head)-sharded x{world}, no collective",
             "l2_policy": "inputs+outputs per step (Q,K,V,O) exceed the 126 MB L2; no flush"}
 
@@ -260,8 +277,10 @@ def run_ours(args, rank, local_rank, world):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     b, h, lq, lk, layout = WORKLOADS[args.workload]
+    opts = WORKLOAD_OPTIONS.get(args.workload, {})
+    causal, hk = bool(opts.get("causal", False)), int(opts.get("heads_kv", h))
     shape_q = (b, h, lq, HEAD_DIM) if layout == "bhld" else (b, lq, h, HEAD_DIM)
-    shape_k = (b, h, lk, HEAD_DIM) if layout == "bhld" else (b, lk, h, HEAD_DIM)
+    shape_k = (b, hk, lk, HEAD_DIM) if layout == "bhld" else (b, lk, hk, HEAD_DIM)
 
     # host-side inputs (pinned) are the source for the e2e leg and for the resident copies
     g = torch.Generator().manual_seed(1234 + rank)
@@ -288,7 +307,7 @@ def run_ours(args, rank, local_rank, world):
 
     # ---- device-resident timing
     for _ in range(args.warmup):
-        ops.attention(q, k, v, layout=layout, out=o)
+        ops.attention(q, k, v, layout=layout, out=o, causal=causal)
     barrier()
     _native.device_check()
     launches0 = _native.launch_count()
@@ -300,7 +319,7 @@ def run_ours(args, rank, local_rank, world):
     evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     evs[0].record(stream)
     for i in range(args.steps):
-        ops.attention(q, k, v, layout=layout, out=o)
+        ops.attention(q, k, v, layout=layout, out=o, causal=causal)
         evs[i + 1].record(stream)
     barrier()
     total_ms = evs[0].elapsed_time(evs[-1])
@@ -310,10 +329,10 @@ def run_ours(args, rank, local_rank, world):
     clocks = sampler.stop() if rank == 0 else None
     total_ms = max_over_ranks(total_ms)
     ms_per_step = total_ms / args.steps
-    step_flops_global = flops(b * world, h, lq, lk)
+    step_flops_global = flops(b * world, h, lq, lk, causal)
     value = step_flops_global / (ms_per_step * 1e-3) / 1e12
     kernel_ms = statistics.mean(per_launch)
-    achieved = flops(b, h, lq, lk) / (kernel_ms * 1e-3) / 1e12
+    achieved = flops(b, h, lq, lk, causal) / (kernel_ms * 1e-3) / 1e12
 
     # ---- end to end: host buffers in, host buffer out, through the public API. Every step copies
     # its Q, K, V from pinned host memory and its O back; HostPipeline overlaps the copies of
@@ -321,7 +340,7 @@ def run_ours(args, rank, local_rank, world):
     from b200_attention_b200.pipeline import HostPipeline
 
     e2e_steps = max(4, min(args.steps, 12))
-    pipe = HostPipeline(shape_q, shape_k, layout=layout, device=dev)
+    pipe = HostPipeline(shape_q, shape_k, layout=layout, device=dev, causal=causal)
     for _ in range(2):
         pipe.submit(q_h, k_h, v_h, o_h)
     pipe.finish()
@@ -347,12 +366,12 @@ def run_ours(args, rank, local_rank, world):
 
     # ---- the reference project's final kernel on the same GPU and inputs (rank 0, BHLD only)
     k18 = None
-    if rank == 0 and not args.no_k18:
+    if rank == 0 and not args.no_k18 and not opts:  # the reference's final kernel is dense and ungrouped
         k18 = time_k18(torch, q, k, v, layout, args)
     # ---- CPU baseline on a bounded sample (rank 0, single-GPU runs only)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        tf, heads, secs, cores = cpu_sdpa_sample(b, h, lq, lk, budget_s=args.cpu_budget)
+        tf, heads, secs, cores = cpu_sdpa_sample(b, h, lq, lk, budget_s=args.cpu_budget, causal=causal)
         cpu = {"value": tf, "unit": "TFLOPS", "cores": cores, "kind": "reference",
                "sample": (f"torch scaled_dot_product_attention (math backend, fp32, CPU: the call the "
                           f"reference checks its kernels against), {heads} of {b * h} (batch, head) "
