@@ -1,7 +1,7 @@
 /*
- * b200_attention.h — C ABI of libb200attn.so: dense, non-causal, forward scaled-dot-product
- * attention for NVIDIA B200 (sm_100a). bf16 Q/K/V in, bf16 O out, optional fp32 LSE,
- * head_dim 128. Plain pointers and sizes only; no torch types. Every entry point returns
+ * b200_attention.h — C ABI of libb200attn.so: dense forward scaled-dot-product attention for
+ * NVIDIA B200 (sm_100a): non-causal, or with a causal mask; optionally with grouped K/V heads.
+ * bf16 Q/K/V in, bf16 O out, optional fp32 LSE, head_dim 128. Plain pointers and sizes only; no torch types. Every entry point returns
  * a b200attn_status (0 = success) and never throws or aborts.
  *
  * Which entry point replaces which interface of the reference project
@@ -23,6 +23,11 @@
  *                          sequence-parallel K/V ring. The reference has no counterpart for
  *                          the extra arguments (its scale is fixed at 1/sqrt(128),
  *                          18_tma_l2_promotion.cu:654, and it has no LSE or multi-GPU path).
+ *                          Its `causal` / `heads_kv` fields cover the operator of the
+ *                          reference's research launcher
+ *                          `attention_tcgen05_causal_gqa_2cta_launch(Q, K, V, O, LSE, counter, B,
+ *                          Sq, Skv, Hq, Hkv, softmax_scale, stream)`
+ *                          (research/causal_gqa_2cta.cu:1131-1137).
  */
 #ifndef B200_ATTENTION_H_
 #define B200_ATTENTION_H_
