@@ -410,12 +410,19 @@ __device__ __forceinline__ ItemCoord decode_item(const FwdParams& p, int item) {
 
 // K/V tiles an item visits: all of them, or with a causal mask (key j is visible to row i iff
 // j <= i + causal_off, causal_off = len_kv - len_q >= 0) those up to its last row's diagonal.
+// Per Q tile q of the item: its last row decides (a Q tile past len_q counts as one row, it
+// computes rows nobody stores). The second Q tile visits as many tiles as the first or one more.
+template <bool kCausal>
+__device__ __forceinline__ int q_tile_tiles(const FwdParams& p, int row0, int q) {
+  if (!kCausal) return p.kv_tiles;
+  const int first_row = row0 + q * kBlockM;
+  const int last_row = min(first_row + kBlockM - 1, max(p.len_q - 1, first_row));
+  return min(p.kv_tiles, (last_row + p.causal_off) / kBlockN + 1);
+}
+// The K/V stream of the item: what its second (longer) Q tile visits.
 template <bool kCausal>
 __device__ __forceinline__ int item_tiles(const FwdParams& p, int row0) {
-  if (!kCausal) return p.kv_tiles;
-  const int last_row = min(row0 + kItemRows, p.len_q) - 1;
-  const int tiles = (last_row + p.causal_off + kBlockN) / kBlockN;  // ceil((last_row + off + 1) / 128)
-  return min(p.kv_tiles, tiles);
+  return q_tile_tiles<kCausal>(p, row0, kQTilesPerItem - 1);
 }
 
 // ---- TMA producer -------------------------------------------------------------------------
@@ -525,9 +532,110 @@ __device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CU
 }
 
 // ---- MMA issuer ---------------------------------------------------------------------------
+// Causal form of the MMA issuer (below is the dense one, which it follows step by step). The two
+// Q tiles of an item walk the same K/V stream, but the first one stops a tile earlier when the
+// stream's last tile lies wholly behind its diagonal: it then takes no part in that tile (no
+// scores, no softmax, no PV), and its accumulator is handed to the epilogue a tile earlier.
+__device__ void ws_mma_role_causal(const FwdParams& p, uint32_t smem_q, uint32_t smem_kv,
+                                   uint32_t bar0, uint32_t tmem_base, uint32_t lead, WaitCtx& w) {
+  auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
+  uint32_t slot = 0, full_parity = 0;  // the (V, K) pair to wait for next: see ws_load_role
+  uint32_t q_full_parity = 0;
+  uint32_t p_parity[kQTilesPerItem] = {0, 0};  // one phase per tile the Q tile takes part in
+  uint32_t o_free_parity = 1;  // passes on the fresh barrier: both accumulators start out free
+  bool ok = true;
+  bool k_ready = false;
+
+  for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
+    const int row0 = decode_item<true>(p, item).row0;
+    int Tq[kQTilesPerItem];
+#pragma unroll
+    for (int q = 0; q < kQTilesPerItem; ++q) Tq[q] = q_tile_tiles<true>(p, row0, q);
+    const int T = Tq[kQTilesPerItem - 1];
+    w.item = item;
+    w.tile = 0;
+    // ---- tile 0 scores for both Q tiles
+    if (!k_ready) {
+      if (!(ok = w.wait_issue(bar(kBarPairFull + slot), full_parity, 200))) break;
+      slot ^= 1u;
+      if (slot == 0) full_parity ^= 1u;
+      k_ready = true;
+    }
+    {
+      const uint32_t k_smem = smem_kv + (slot ^ 1u) * kPairBytes + kTileBytes;
+#pragma unroll
+      for (int q = 0; q < kQTilesPerItem; ++q) {
+        if (!(ok = w.wait_issue(bar(kBarQFull + q), q_full_parity, 201 + q))) break;
+        tc_fence_after_sync();
+        issue_qk(lead, tmem_base + q * kBlockN, smem_q + q * kTileBytes, k_smem);
+        umma_commit_lead(lead, bar(kBarSFull + q));
+        if (Tq[q] == 1) umma_commit_lead(lead, bar(kBarQEmpty + q));
+      }
+    }
+    if (!ok) break;
+    // also covers the PV of the previous item that read the V half of this pair
+    umma_commit_lead(lead, bar(kBarPairEmpty + (slot ^ 1u)));
+    q_full_parity ^= 1u;
+
+    for (int i = 0; ok && i < T; ++i) {
+      w.tile = i;
+      // V_i and K_{i+1} (or K_0 of this CTA's next item) in one phase
+      if (!(ok = w.wait_issue(bar(kBarPairFull + slot), full_parity, 210))) break;
+      const uint32_t v_smem = smem_kv + slot * kPairBytes;
+      const uint32_t k_smem = v_smem + kTileBytes;
+      const uint32_t pair_empty = bar(kBarPairEmpty + slot);
+      slot ^= 1u;
+      if (slot == 0) full_parity ^= 1u;
+#pragma unroll
+      for (int q = 0; q < kQTilesPerItem; ++q) {
+        if (i < Tq[q]) {
+          const uint32_t s_tmem = tmem_base + q * kBlockN;
+          const uint32_t o_tmem = tmem_base + kQTilesPerItem * kBlockN + q * kHeadDim;
+          if (i == 0) {
+            // the previous item's epilogue must have read O_q out before it is overwritten
+            if (!(ok = w.wait_issue(bar(kBarOFree + q), o_free_parity, 240 + q))) break;
+          }
+          if (!(ok = w.wait_issue(bar(kBarPReady + q), p_parity[q], 220 + q))) break;
+          tc_fence_after_sync();
+          issue_pv(lead, o_tmem, s_tmem, v_smem, 0, kPartAKSteps, /*accumulate_first=*/i > 0);
+          if (kPartAChunks < 4) {
+            if (!(ok = w.wait_issue(bar(kBarPFull + q), p_parity[q], 225 + q))) break;
+            tc_fence_after_sync();
+            issue_pv(lead, o_tmem, s_tmem, v_smem, kPartAKSteps, kBlockN / 16, /*accumulate_first=*/true);
+          }
+          p_parity[q] ^= 1u;
+          if (i + 1 < Tq[q]) {
+            issue_qk(lead, s_tmem, smem_q + q * kTileBytes, k_smem);
+            umma_commit_lead(lead, bar(kBarSFull + q));
+            if (i + 2 == Tq[q]) umma_commit_lead(lead, bar(kBarQEmpty + q));
+          } else {
+            umma_commit_lead(lead, bar(kBarPvDone + q));
+          }
+        }
+        // the pair is free once the longer Q tile is through with it (K_{i+1} only if there is one)
+        if (q == kQTilesPerItem - 1 && i + 1 < T) umma_commit_lead(lead, pair_empty);
+      }
+    }
+    o_free_parity ^= 1u;
+  }
+
+  if (!ok || w.aborted()) {
+    // Leaving early: make sure nothing this warp issued is still running before TMEM goes.
+    umma_commit_lead(lead, bar(kBarDrain));
+    const uint64_t t0 = global_timer_ns();
+    while (!mbar_try_wait(bar(kBarDrain), 0, 1000)) {
+      if (global_timer_ns() - t0 > w.limit_ns) break;
+    }
+  }
+}
+
 template <bool kCausal>
 __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_kv, uint32_t bar0,
                             uint32_t tmem_base, uint32_t lead, WaitCtx& w) {
+  if (kCausal) {
+    ws_mma_role_causal(p, smem_q, smem_kv, bar0, tmem_base, lead, w);
+    return;
+  }
   // Run by the whole warp with uniform control flow; `lead` marks the one lane that issues.
   auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
   // K/V arrive in pairs (V of one tile with K of the next): see ws_load_role.
@@ -543,7 +651,7 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
   PROF_DECL(8);  // 0 other, 1 wait pair, 3 wait P (+O_FREE), 4 issue PV, 5 issue QK, 6 commits
 
   for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
-    const int T = kCausal ? item_tiles<true>(p, decode_item<true>(p, item).row0) : p.kv_tiles;
+    const int T = p.kv_tiles;
     w.item = item;
     w.tile = 0;
     // ---- tile 0 scores for both Q tiles
@@ -735,7 +843,7 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
     float l = 0.0f;     // running sum of 2^(s - m)
     // causal: this row sees keys 0 .. row + causal_off; its Q tile's first row sees the fewest
     const int row0 = kCausal ? decode_item<true>(p, item).row0 : 0;
-    const int T = item_tiles<kCausal>(p, row0);
+    const int T = q_tile_tiles<kCausal>(p, row0, q);
     const int tile_limit = row0 + q * kBlockM + p.causal_off;  // last key the tile's first row sees
     const int row_limit = tile_limit + r;                      // last key this row sees
     for (int i = 0; i < T; ++i) {
