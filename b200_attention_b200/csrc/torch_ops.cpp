@@ -43,11 +43,14 @@ b200attn_operand operand(const at::Tensor& t, bool bshd) {
 // Shared body: Q [B,H,Lq,128] (bhld) or [B,Lq,H,128] (bshd); returns (O, LSE or undefined).
 std::tuple<at::Tensor, at::Tensor> run(const at::Tensor& Q_in, const at::Tensor& K_in,
                                        const at::Tensor& V_in, double scale, bool bshd,
-                                       bool want_lse, int64_t kernel) {
+                                       bool want_lse, int64_t kernel, bool causal = false) {
   check_common(Q_in, K_in, V_in);
   const int l_axis = bshd ? 1 : 2, h_axis = bshd ? 2 : 1;
   TORCH_CHECK(Q_in.size(0) == K_in.size(0), "Q and K/V must have the same batch size");
-  TORCH_CHECK(Q_in.size(h_axis) == K_in.size(h_axis), "Q and K/V must have the same number of heads");
+  TORCH_CHECK(K_in.size(h_axis) >= 1 && Q_in.size(h_axis) % K_in.size(h_axis) == 0,
+              "the number of Q heads must be a multiple of the number of K/V heads");
+  TORCH_CHECK(!causal || K_in.size(l_axis) >= Q_in.size(l_axis),
+              "causal attention needs at least as many keys as queries (bottom-right aligned mask)");
   TORCH_CHECK(Q_in.size(3) == 128 && K_in.size(3) == 128, "head_dim must be 128");
   TORCH_CHECK(Q_in.size(l_axis) >= 1 && K_in.size(l_axis) >= 1, "sequence lengths must be positive");
   constexpr int64_t kMaxInt = std::numeric_limits<int>::max();
@@ -92,6 +95,8 @@ std::tuple<at::Tensor, at::Tensor> run(const at::Tensor& Q_in, const at::Tensor&
   a.lse = want_lse ? LSE.data_ptr<float>() : nullptr;
   a.softmax_scale = float(scale);
   a.kernel = int(kernel);
+  a.causal = causal ? 1 : 0;
+  a.heads_kv = int(K.size(h_axis));
   a.stream = c10::cuda::getCurrentCUDAStream(Q.device().index()).stream();
   check_rc(b200attn_forward(&a));
   return {O, LSE};
@@ -111,6 +116,14 @@ std::tuple<at::Tensor, at::Tensor> sdpa_lse(const at::Tensor& Q, const at::Tenso
   return run(Q, K, V, scale, bshd, /*want_lse=*/true, kernel);
 }
 
+// Causal attention with grouped K/V heads on token-major tensors, the call shape of the
+// reference's research launcher (research/causal_gqa_2cta.cu:1131-1137): Q [B, Sq, Hq, 128],
+// K, V [B, Skv, Hkv, 128], returns (O [B, Sq, Hq, 128], LSE [B, Hq, Sq]).
+std::tuple<at::Tensor, at::Tensor> sdpa_causal_gqa(const at::Tensor& Q, const at::Tensor& K,
+                                                   const at::Tensor& V, double scale) {
+  return run(Q, K, V, scale, /*bshd=*/true, /*want_lse=*/true, 0, /*causal=*/true);
+}
+
 // Raises if a kernel launched earlier on the current device left early. The caller must have
 // synchronised the stream it launched on.
 void device_check() {
@@ -125,5 +138,6 @@ TORCH_LIBRARY(b200_attention_b200, m) {
   m.def("sdpa_bshd(Tensor Q, Tensor K, Tensor V) -> Tensor", &sdpa_bshd);
   m.def("sdpa_lse(Tensor Q, Tensor K, Tensor V, float scale, bool bshd, int kernel) -> (Tensor, Tensor)",
         &sdpa_lse);
+  m.def("sdpa_causal_gqa(Tensor Q, Tensor K, Tensor V, float scale) -> (Tensor, Tensor)", &sdpa_causal_gqa);
   m.def("device_check() -> ()", &device_check);
 }

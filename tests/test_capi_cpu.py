@@ -101,7 +101,7 @@ def test_torch_shim_registers_reference_op_names(native_built):
 
     torch.ops.load_library(str(native_built["torch_ops"]))
     ops = torch.ops.b200_attention_b200
-    for name in ("sdpa", "sdpa_bshd", "sdpa_lse", "device_check"):
+    for name in ("sdpa", "sdpa_bshd", "sdpa_lse", "sdpa_causal_gqa", "device_check"):
         assert hasattr(ops, name)
     x = torch.zeros(1, 1, 256, 128, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="must be CUDA tensors"):

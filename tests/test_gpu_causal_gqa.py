@@ -118,3 +118,22 @@ def test_rejections(ops):
         ops.attention(q, k2, k2, kernel=1)
     with pytest.raises(RuntimeError, match="warp-specialised"):
         ops.attention(q, q, q, causal=True, kernel=1)
+
+
+def test_torch_op_causal_gqa(native_built):
+    """The shim's op with the call shape of the reference's research launcher: token-major Q with
+    Hq heads, K/V with Hkv heads, returns O token-major and LSE [B, Hq, S]."""
+    from b200_attention_b200 import _native
+
+    torch.ops.load_library(str(native_built["torch_ops"]))
+    q, k, v = O.make_inputs_benchmark(2, 8, 384, 384, seed=51)  # BSHD
+    kg, vg = k[:, :, ::4].contiguous(), v[:, :, ::4].contiguous()
+    o, lse = torch.ops.b200_attention_b200.sdpa_causal_gqa(q.cuda(), kg.cuda(), vg.cuda(), 0.0)
+    torch.cuda.synchronize()
+    _native.device_check()
+    assert o.shape == q.shape and lse.shape == (2, 8, 384)
+    o_ref, lse_ref = O.sdpa_explicit(O.to_bhld(q), O.to_bhld(kg), O.to_bhld(vg), causal=True)
+    O.assert_within_contract(O.compare(O.to_bhld(o.cpu()), o_ref, lse.cpu(), lse_ref))
+    with pytest.raises(RuntimeError, match="multiple of the number of K/V heads"):
+        torch.ops.b200_attention_b200.sdpa_causal_gqa(q.cuda(), k[:, :, :3].contiguous().cuda(),
+                                                      v[:, :, :3].contiguous().cuda(), 0.0)
