@@ -80,8 +80,8 @@ SEQUENCE_WORKLOADS = {
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu summary of the
-# workload (profiles/attn_fwd_ws_kernel_main_B4_H16_L8192.md); None where nothing was captured.
-NCU_TRAFFIC_BYTES = {"main": 515.5e6}
+# workload (profiles/attn_fwd_ws_kernel_*.md); None where nothing was captured.
+NCU_TRAFFIC_BYTES = {"main": 515.5e6, "dit_cross": 155.0e6, "causal": 659.0e6}
 
 
 def flops(b, h, lq, lk, causal=False):
