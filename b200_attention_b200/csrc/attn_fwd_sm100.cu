@@ -1,19 +1,22 @@
-// Dense, non-causal forward attention for sm_100a: O = softmax(Q K^T * scale) V, bf16 in,
-// bf16 out, fp32 accumulation, optional fp32 LSE, head_dim 128.
+// Dense forward attention for sm_100a: O = softmax(Q K^T * scale) V, bf16 in, bf16 out, fp32
+// accumulation, optional fp32 LSE, head_dim 128; optionally with a causal mask and with grouped
+// K/V heads.
 //
 // Two kernels share the operand layout, descriptors and epilogue:
 //
-//   attn_fwd_ws_kernel      the production kernel. Persistent CTAs (one per SM), 16 warps:
-//                             warps 0-3   softmax for Q tile 0 (one query row per thread)
+//   attn_fwd_ws_kernel      the production kernel (a template on the causal mask). Persistent
+//                           CTAs (one per SM), 16 warps:
+//                             warps 0-3   softmax for Q tile 0 (one query row per thread); also
+//                                         the rare rebase of the O accumulator when a row's
+//                                         reference maximum has to move
 //                             warps 4-7   softmax for Q tile 1
-//                             warps 8-11  correction: rescales the O accumulators when a row
-//                                         maximum moves, and runs the epilogue (normalise,
-//                                         merge with a previous partial, store O / LSE)
+//                             warps 8-11  epilogue: normalise, merge with a previous partial,
+//                                         store O / LSE
 //                             warp 12     issues every tcgen05.mma
 //                             warp 13     issues every TMA load
 //                             warps 14-15 only give their registers away
-//                           Q tiles, and a ring of K / V tiles, sit in 128-byte-swizzled shared
-//                           memory; S = Q K^T, the bf16 P that overwrites it, and both O
+//                           Q tiles, and a ring of (V, K) tile pairs, sit in 128-byte-swizzled
+//                           shared memory; S = Q K^T, the bf16 P that overwrites it, and both O
 //                           accumulators live in TMEM (4 x 128 columns).
 //
 //   attn_fwd_serial_kernel  bring-up / cross-check kernel: one CTA per 128 query rows, every
