@@ -1,0 +1,133 @@
+"""GPU tests at the full benchmark sizes, through properties that do not need a full-size CPU
+result: sampled query rows against the CPU oracle (a row of attention depends on its own query
+and on all keys and values, which the oracle handles for a few hundred rows at a time), rows of
+softmax sum to one (V = 1 gives O = 1), invariance under a permutation of the keys, and two
+K/V halves chained through the partial-state epilogue equal to one call."""
+
+import pytest
+import torch
+
+from oracle import sdpa_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+MAIN = (4, 16, 8192, 8192)  # the headline configuration: B, H, Lq, Lk
+
+
+@pytest.fixture(scope="module")
+def ops(native_built):
+    if not torch.cuda.is_available():
+        pytest.fail("these tests need a CUDA device")
+    from b200_attention_b200 import _native, ops
+
+    _native.lib()
+    return ops
+
+
+@pytest.fixture(scope="module")
+def main_inputs():
+    b, h, lq, lk = MAIN
+    g = torch.Generator().manual_seed(2024)
+    q = torch.randn(b, h, lq, 128, generator=g).to(torch.bfloat16)
+    k = torch.randn(b, h, lk, 128, generator=g).to(torch.bfloat16)
+    v = torch.randn(b, h, lk, 128, generator=g).to(torch.bfloat16)
+    return q, k, v
+
+
+def check_sampled_rows(o, lse, q, k, v, heads, rows, *, causal=False, group=1):
+    """o, lse: GPU results [B,H,Lq,128] / [B,H,Lq]; q, k, v: CPU inputs (BHLD). Compares the given
+    rows of the given (batch, head) pairs with the explicit oracle."""
+    lq, lk = q.shape[2], k.shape[2]
+    for (b, h) in heads:
+        kh, vh = k[b:b + 1, h // group:h // group + 1], v[b:b + 1, h // group:h // group + 1]
+        qs = q[b:b + 1, h:h + 1, rows]
+        s = torch.matmul(qs.float(), kh.float().transpose(-1, -2)) * O.default_scale()
+        if causal:
+            cols = torch.arange(lk).view(1, 1, 1, -1)
+            s = s.masked_fill(cols > rows.view(1, 1, -1, 1) + (lk - lq), float("-inf"))
+        lse_ref = torch.logsumexp(s, dim=-1)
+        o_ref = torch.matmul(torch.exp(s - lse_ref.unsqueeze(-1)), vh.float())
+        stats = O.compare(o[b:b + 1, h:h + 1, rows].cpu(), o_ref, lse[b:b + 1, h:h + 1, rows].cpu(), lse_ref)
+        O.assert_within_contract(stats)
+
+
+def sample_rows(lq, n, seed):
+    g = torch.Generator().manual_seed(seed)
+    rows = torch.randperm(lq, generator=g)[:n]
+    # always include the first and last rows and both sides of a work-item boundary
+    return torch.unique(torch.cat([rows, torch.tensor([0, 127, 128, 255, 256, lq - 257, lq - 256, lq - 1])]))
+
+
+def test_main_config_sampled_rows_match_oracle(ops, main_inputs):
+    from b200_attention_b200 import _native
+
+    q, k, v = main_inputs
+    o, lse = ops.attention(q.cuda(), k.cuda(), v.cuda(), return_lse=True)
+    torch.cuda.synchronize()
+    _native.device_check()
+    assert bool(torch.isfinite(o.float()).all()) and bool(torch.isfinite(lse).all())
+    check_sampled_rows(o, lse, q, k, v, heads=[(0, 0), (1, 7), (3, 15)], rows=sample_rows(8192, 192, 1))
+
+
+def test_main_config_rows_of_softmax_sum_to_one(ops, main_inputs):
+    q, k, _ = main_inputs
+    ones = torch.ones(MAIN[0], MAIN[1], MAIN[3], 128, dtype=torch.bfloat16, device="cuda")
+    o = ops.attention(q.cuda(), k.cuda(), ones)
+    torch.cuda.synchronize()
+    # P is rounded to bf16 before PV while the row sum is kept in fp32: |O - 1| stays within the
+    # bf16 rounding of P (2^-9 relative), far inside the output tolerance
+    assert float((o.float() - 1.0).abs().max()) <= 4e-3
+
+
+def test_main_config_is_invariant_under_key_permutation(ops, main_inputs):
+    q, k, v = main_inputs
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    o1, lse1 = ops.attention(qd, kd, vd, return_lse=True)
+    perm = torch.randperm(MAIN[3], generator=torch.Generator().manual_seed(3)).cuda()
+    o2, lse2 = ops.attention(qd, kd[:, :, perm].contiguous(), vd[:, :, perm].contiguous(), return_lse=True)
+    torch.cuda.synchronize()
+    # the same sums in another order and another tiling: differences are rounding only
+    assert float((lse1 - lse2).abs().max()) <= 1e-4
+    d = (o1.float() - o2.float()).abs()
+    assert float(d.max()) <= O.O_MAX_ABS and float(d.mean()) <= 2e-4
+
+
+def test_main_config_two_kv_halves_chain_to_the_full_result(ops, main_inputs):
+    q, k, v = main_inputs
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    full, lse_full = ops.attention(qd, kd, vd, return_lse=True)
+    b, h, lq, lk = MAIN
+    scratch = (torch.empty(b, h, lq, 128, dtype=torch.float32, device="cuda"),
+               torch.empty(b, h, lq, dtype=torch.float32, device="cuda"))
+    half = lk // 2
+    ops.attention(qd, kd[:, :, :half], vd[:, :, :half], partial=scratch, partial_emit=True)
+    o, lse = ops.attention(qd, kd[:, :, half:], vd[:, :, half:], partial=scratch, partial_merge=True,
+                           return_lse=True)
+    torch.cuda.synchronize()
+    assert float((lse - lse_full).abs().max()) <= 1e-4
+    d = (o.float() - full.float()).abs()
+    assert float(d.max()) <= O.O_MAX_ABS and float(d.mean()) <= 2e-4
+
+
+def test_main_config_causal_grouped_sampled_rows(ops, main_inputs):
+    from b200_attention_b200 import _native
+
+    q, k, v = main_inputs
+    kg, vg = k[:, ::4].contiguous(), v[:, ::4].contiguous()  # 4 K/V heads for 16 query heads
+    o, lse = ops.attention(q.cuda(), kg.cuda(), vg.cuda(), causal=True, return_lse=True)
+    torch.cuda.synchronize()
+    _native.device_check()
+    check_sampled_rows(o, lse, q, kg, vg, heads=[(0, 1), (2, 6), (3, 15)], rows=sample_rows(8192, 192, 2),
+                       causal=True, group=4)
+
+
+def test_video_self_attention_shape_sampled_rows(ops):
+    """B=1, H=12, Lq=Lk=32768, token-major in place, RMS-normalised Q/K."""
+    from b200_attention_b200 import _native
+
+    q, k, v = O.make_inputs_video_dit(12, 32768, 32768, seed=9)  # BSHD
+    o, lse = ops.attention(q.cuda(), k.cuda(), v.cuda(), layout="bshd", return_lse=True)
+    torch.cuda.synchronize()
+    _native.device_check()
+    check_sampled_rows(o.transpose(1, 2), lse, O.to_bhld(q), O.to_bhld(k), O.to_bhld(v),
+                       heads=[(0, 0), (0, 11)], rows=sample_rows(32768, 128, 4))
