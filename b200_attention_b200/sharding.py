@@ -67,11 +67,25 @@ def imbalance(batch: int, heads: int, world: int) -> float:
     return most / (total / world)
 
 
+def launches_of(ranges: Sequence[HeadRange], heads: int) -> List[Tuple[int, int, int, int]]:
+    """(batch_begin, batch_end, head_begin, head_end) per launch: consecutive batch entries owned
+    with all their heads go into one launch (fewer, fuller waves of work items), a partial head
+    range is a launch of its own."""
+    out: List[Tuple[int, int, int, int]] = []
+    for r in ranges:
+        full = r.head_begin == 0 and r.head_end == heads
+        if full and out and out[-1][2] == 0 and out[-1][3] == heads and out[-1][1] == r.batch:
+            out[-1] = (out[-1][0], r.batch + 1, 0, heads)
+        else:
+            out.append((r.batch, r.batch + 1, r.head_begin, r.head_end))
+    return out
+
+
 def run_shard(q, k, v, ranges: Sequence[HeadRange], *, layout: str = "bhld", out=None,
               softmax_scale: float = 0.0, return_lse: bool = False):
     """Runs attention for `ranges` of q/k/v (full tensors resident on this rank's GPU) and
-    writes the matching slices of `out` (allocated like q if None). One launch per range, no
-    copies: a range is a strided view. Returns out (and LSE [B, H, Lq] with only the owned
+    writes the matching slices of `out` (allocated like q if None). One launch per run of whole
+    batch entries and one per partial head range (`launches_of`), no copies: a slice is a strided view. Returns out (and LSE [B, H, Lq] with only the owned
     slices written, if asked)."""
     import torch
 
@@ -84,12 +98,12 @@ def run_shard(q, k, v, ranges: Sequence[HeadRange], *, layout: str = "bhld", out
     if return_lse:
         lq = q.size(2) if layout == "bhld" else q.size(1)
         lse = torch.zeros(q.size(0), q.size(h_axis), lq, dtype=torch.float32, device=q.device)
-    for r in ranges:
-        sl = [slice(r.batch, r.batch + 1), slice(None), slice(None), slice(None)]
-        sl[h_axis] = slice(r.head_begin, r.head_end)
+    for b0, b1, h0, h1 in launches_of(ranges, q.size(h_axis)):
+        sl = [slice(b0, b1), slice(None), slice(None), slice(None)]
+        sl[h_axis] = slice(h0, h1)
         sl = tuple(sl)
         res = ops.attention(q[sl], k[sl], v[sl], layout=layout, out=out[sl],
                             softmax_scale=softmax_scale, return_lse=return_lse)
         if return_lse:
-            lse[r.batch:r.batch + 1, r.head_begin:r.head_end] = res[1]
+            lse[b0:b1, h0:h1] = res[1]
     return (out, lse) if return_lse else out

@@ -22,7 +22,9 @@ is `batch * N`. Rank 0 prints one JSON line.
 `--impl reference` times the CPU arm alone (rank 0 only) and prints the same line shape.
 `--workload dit_1056` times the video-DiT call sequence (528 self- and 528 cross-attention
 launches per step) as one CUDA-graph replay per step, with the eager time beside it;
-`--workload sp_ring` the sequence-parallel K/V ring (needs --gpus >= 2).
+`--workload sp_ring` the sequence-parallel K/V ring (needs --gpus >= 2); `--workload main_strong`
+splits the headline problem itself over the ranks (strong scaling; the default `main` gives every
+rank its own copy of it, weak scaling).
 """
 
 from __future__ import annotations
@@ -69,6 +71,11 @@ WORKLOAD_OPTIONS = {
 RING_WORKLOADS = {
     "sp_ring": (1, 32, 131072),
     "sp_ring_small": (1, 8, 16384),
+}
+# Strong scaling of one fixed problem: the (batch, head) slices of the GLOBAL shape are dealt to the
+# ranks by sharding.plan (contiguous, near-equal pieces), every rank launches only its own.
+STRONG_WORKLOADS = {
+    "main_strong": (4, 16, 8192, 8192),
 }
 # Video-DiT call sequence: per generation 528 self-attention calls (B, H, L, L) and 528
 # cross-attention calls (B, H, L, Lc), issued back to back on one stream; a step is the whole
@@ -636,6 +643,108 @@ def run_sequence(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+def run_strong(args, rank, local_rank, world):
+    """The headline problem (global B=4, H=16) split by (batch, head) over the ranks: strong
+    scaling, no data-path collective. value = global FLOPs / max-over-ranks time."""
+    import torch
+    import torch.distributed as dist
+
+    from b200_attention_b200 import _native, sharding
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    b, h, lq, lk = STRONG_WORKLOADS[args.workload]
+    ranges = sharding.plan(b, h, world, rank)
+    g = torch.Generator().manual_seed(1234)
+    q_h = torch.randn(b, h, lq, HEAD_DIM, generator=g).to(torch.bfloat16).pin_memory()
+    k_h = torch.randn(b, h, lk, HEAD_DIM, generator=g).to(torch.bfloat16).pin_memory()
+    v_h = torch.randn(b, h, lk, HEAD_DIM, generator=g).to(torch.bfloat16).pin_memory()
+    o_h = torch.empty_like(q_h).pin_memory()
+    q, k, v = q_h.to(dev), k_h.to(dev), v_h.to(dev)   # inputs resident on every GPU before timing
+    o = torch.empty_like(q)
+    stream = torch.cuda.current_stream(dev)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for _ in range(args.warmup):
+        sharding.run_shard(q, k, v, ranges, out=o)
+    barrier()
+    _native.device_check()
+    launches0 = _native.launch_count()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        sharding.run_shard(q, k, v, ranges, out=o)
+    e1.record(stream)
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    launches = _native.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    _native.device_check()
+    # end to end: this rank's slices from pinned host memory in, its slices of O back out
+    e2e_steps = max(2, min(args.steps, 6))
+    barrier()
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        for r in ranges:
+            sl = (slice(r.batch, r.batch + 1), slice(r.head_begin, r.head_end))
+            for d, src in ((q, q_h), (k, k_h), (v, v_h)):
+                d[sl].copy_(src[sl], non_blocking=True)
+        sharding.run_shard(q, k, v, ranges, out=o)
+        for r in ranges:
+            sl = (slice(r.batch, r.batch + 1), slice(r.head_begin, r.head_end))
+            o_h[sl].copy_(o[sl], non_blocking=True)
+    e1.record(stream)
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
+    total = flops(b, h, lq, lk)
+    if rank == 0:
+        peaks = measured_peaks()
+        value = total / (ms * 1e-3) / 1e12
+        units = sharding.units_of(ranges)
+        tile_bytes = lq * HEAD_DIM * 2
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": (f"{args.workload}: dense non-causal attention forward, GLOBAL B={b} H={h} "
+                                    f"Lq={lq} Lk={lk} D=128 bf16 N(0,1), {b * h} (batch, head) slices dealt to "
+                                    f"{world} rank(s), {units} on rank 0"),
+                       "global_batch": b, "heads": h, "len_q": lq, "len_kv": lk, "head_dim": HEAD_DIM,
+                       "layout": "bhld", "parallelism": f"(batch,head)-sharded x{world}, no collective",
+                       "work_items_per_gpu": units * ((lq + 255) // 256),
+                       "l2_policy": "per-step operands exceed the 126 MB L2 up to 4 GPUs; no flush"},
+            "pct_of_bf16_peak": 100.0 * value / world / peaks["bf16_tflops"],
+            "roofline": {"bound": "tensor", "achieved": value / world, "peak": peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": value / world / peaks["bf16_tflops"],
+                         "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "traffic": None},
+            "e2e": {"value": total / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS",
+                    "h2d_bytes_per_step": 3 * b * h * tile_bytes, "d2h_bytes_per_step": b * h * tile_bytes,
+                    "ms_per_step": e2e_ms},
+            "gpu_launches": int(launches), "clocks": clocks, "cpu_baseline": None, "k18_same_gpu": None,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def time_k18(torch, q, k, v, layout, args):
     try:
         from oracle import native_refs as R
@@ -673,7 +782,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="main",
-                    choices=sorted(WORKLOADS) + sorted(RING_WORKLOADS) + sorted(SEQUENCE_WORKLOADS))
+                    choices=sorted(WORKLOADS) + sorted(RING_WORKLOADS) + sorted(SEQUENCE_WORKLOADS)
+                    + sorted(STRONG_WORKLOADS))
     ap.add_argument("--no-k18", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=12.0)
@@ -693,6 +803,13 @@ def main():
                                   "the reference project has no sequence-parallel path; use --workload main"}))
             return
         run_ring(args, rank, local_rank, world)
+        return
+    if args.workload in STRONG_WORKLOADS:
+        if args.impl == "reference":
+            args.workload = "main"  # the CPU arm times the same global problem
+            run_reference_arm(args, rank, 1)
+            return
+        run_strong(args, rank, local_rank, world)
         return
     if args.workload in SEQUENCE_WORKLOADS:
         if args.impl == "reference":

@@ -101,6 +101,18 @@ def test_sharding_plan_partitions_every_unit_once(batch, heads, world):
     assert max(counts) - min(counts) <= 1
 
 
+def test_sharding_launches_merge_whole_batch_entries():
+    assert sharding.launches_of(sharding.plan(4, 16, 1, 0), 16) == [(0, 4, 0, 16)]
+    assert sharding.launches_of(sharding.plan(4, 16, 2, 1), 16) == [(2, 4, 0, 16)]
+    assert sharding.launches_of(sharding.plan(4, 16, 8, 3), 16) == [(1, 2, 8, 16)]
+    # 3 x 5 units over 4 ranks: rank 1 owns heads 4 of batch 0 and heads 0..2 of batch 1
+    assert sharding.launches_of(sharding.plan(3, 5, 4, 1), 5) == [(0, 1, 4, 5), (1, 2, 0, 3)]
+    # a rank that owns a partial range, whole entries, and a partial range again
+    ranges = [sharding.HeadRange(0, 3, 5), sharding.HeadRange(1, 0, 5), sharding.HeadRange(2, 0, 5),
+              sharding.HeadRange(3, 0, 2)]
+    assert sharding.launches_of(ranges, 5) == [(0, 1, 3, 5), (1, 3, 0, 5), (3, 4, 0, 2)]
+
+
 def test_sharding_main_config_is_even():
     for world in (1, 2, 4, 8):
         assert sharding.imbalance(4, 16, world) == 1.0
