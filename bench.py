@@ -784,6 +784,8 @@ def main():
     ap.add_argument("--workload", default="main",
                     choices=sorted(WORKLOADS) + sorted(RING_WORKLOADS) + sorted(SEQUENCE_WORKLOADS)
                     + sorted(STRONG_WORKLOADS))
+    ap.add_argument("--layout", default=None, choices=["bhld", "bshd"],
+                    help="override the workload's operand layout (single-launch workloads)")
     ap.add_argument("--no-k18", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=12.0)
@@ -792,6 +794,8 @@ def main():
     args.steps = 100 if args.steps is None else args.steps
     args.warmup = 5 if args.warmup is None else args.warmup
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.layout is not None and args.workload in WORKLOADS:
+        WORKLOADS[args.workload] = WORKLOADS[args.workload][:4] + (args.layout,)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
