@@ -246,6 +246,10 @@ int b200attn_forward(const b200attn_forward_args* a) {
   if ((a->partial_merge != 0 || a->partial_emit != 0) &&
       (a->partial_o == nullptr || a->partial_lse == nullptr))
     return fail(B200ATTN_ERR_INVALID_ARGUMENT, "partial_merge / partial_emit need partial_o and partial_lse");
+  // The kernel derives the mask's diagonal from this call's own len_kv; a chain over K/V shards
+  // would mask every shard as if it started at key 0.
+  if (a->causal != 0 && (a->partial_merge != 0 || a->partial_emit != 0))
+    return fail(B200ATTN_ERR_UNSUPPORTED, "a causal mask cannot be combined with partial_merge / partial_emit");
   if (a->partial_o != nullptr && (reinterpret_cast<uintptr_t>(a->partial_o) & 15u) != 0)
     return fail(B200ATTN_ERR_INVALID_ARGUMENT, "partial_o must be 16-byte aligned");
   if (!(a->softmax_scale == a->softmax_scale) || std::isinf(a->softmax_scale))

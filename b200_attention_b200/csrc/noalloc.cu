@@ -17,13 +17,18 @@
 // In host code the array's name is only a host-side stand-in for the symbol, never a device
 // address, so the address the kernel gets is obtained with cudaGetSymbolAddress, once per
 // device, with that device current, on the first call made on that device. That first call
-// also sets kernel attributes and zeroes the watchdog record; make it before any stream capture.
+// also sets kernel attributes; make it before any stream capture.
 //
 // Every call on a device shares the array and it keeps the previous call's contents. Nothing in
 // the partial-state region has to start at zero (the first K/V chunk of a call overwrites it
-// before any later chunk reads it); the watchdog record must, and is cleared at set-up and
-// whenever a non-zero record has been reported. Two calls whose kernels overlap on the GPU
-// (different streams, or different host threads) race on the array: serialise them.
+// before any later chunk reads it); the watchdog record must: it is zero when the library image
+// is loaded (file-scope device memory starts out zeroed) and is cleared again whenever a
+// non-zero record has been reported. Two calls whose kernels overlap on the GPU (different
+// streams, or different host threads) race on the array: serialise them.
+//
+// A launching call (kv_splits >= 1) only checks arguments and enqueues kernels: no stream query,
+// no copy, no synchronisation. The watchdog record is read back only by a kv_splits == 0 call,
+// which synchronises the stream; that call is refused on a stream that is being captured.
 //
 // The entry point calls no cudaMalloc, cudaFree, cudaHostAlloc or any other allocating routine.
 
@@ -86,9 +91,6 @@ void setup_device(int device, NoAllocDevice* st) {
     st->init_error = "scratch symbol address is null or not 256-byte aligned";
     return;
   }
-  if ((e = cudaMemset(base + kPartialOFloats + kPartialLseFloats, 0, kStatusFloats * sizeof(float))) !=
-      cudaSuccess)
-    return cuda_fail("clearing the watchdog record", e);
   st->scratch = base;
 }
 
@@ -140,9 +142,15 @@ extern "C" B200ATTN_API int b200attn_forward_kv_split_noalloc(const b200attn_for
   int32_t* status = reinterpret_cast<int32_t*>(st->scratch + kPartialOFloats + kPartialLseFloats);
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
 
-  // Report what an earlier call left in the watchdog record, but only when that costs no wait:
-  // the stream has drained, so the 32-byte read-back returns at once.
-  if (cudaStreamQuery(stream) == cudaSuccess) {
+  if (kv_splits == 0) {
+    // Report what earlier calls left in the watchdog record. This is the one place the entry point
+    // waits for the GPU, so it is never done on a stream that is being captured (querying or
+    // synchronising such a stream would invalidate the capture).
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    if ((e = cudaStreamIsCapturing(stream, &capture)) != cudaSuccess) return fail_cuda("cudaStreamIsCapturing", e);
+    if (capture != cudaStreamCaptureStatusNone)
+      return fail(B200ATTN_ERR_INVALID_ARGUMENT,
+                  "kv_splits == 0 reads the watchdog record back and cannot run on a capturing stream");
     int32_t rec[kStatusInts] = {0};
     e = cudaMemcpyAsync(rec, status, sizeof rec, cudaMemcpyDeviceToHost, stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
@@ -156,10 +164,8 @@ extern "C" B200ATTN_API int b200attn_forward_kv_split_noalloc(const b200attn_for
                rec[0], rec[1], rec[2], rec[3], rec[5], rec[6]);
       return fail(rec[0] == kDevWaitTimeout ? B200ATTN_ERR_DEVICE_TIMEOUT : B200ATTN_ERR_DEVICE_FAULT, buf);
     }
-  } else {
-    (void)cudaGetLastError();  // busy (or capturing): skip the check this time
+    return B200ATTN_OK;
   }
-  if (kv_splits == 0) return B200ATTN_OK;
 
   // K/V chunks of whole tiles, as even as possible.
   const int32_t tiles = (a->len_kv + kBlockN - 1) / kBlockN;

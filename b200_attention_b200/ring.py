@@ -8,9 +8,14 @@ kernel works on the previous shard; the kernel's TMA only ever reads local HBM. 
 are chained in the kernel epilogue through an fp32 (O, LSE) scratch (`partial_merge` /
 `partial_emit` of the C ABI): G launches, no merge kernel, no reduction collective.
 
-Ordering is by stream events and two host barriers (inputs ready before anybody pulls, and
-everybody done pulling before inputs may change); no device-side code waits on a peer, and no
-load with cluster multicast is involved anywhere.
+Ordering is by stream events inside a rank and two host barriers between ranks per call: on
+entry every rank first waits (on the host) until the stream that produced its own K/V shard has
+caught up, then all ranks meet, so no peer can pull a shard that is still being written; on exit
+every rank waits for its own pulls and all ranks meet again, so a shard may be rewritten (in
+place, or by an allocator handing the address out again) as soon as `forward` has returned. The
+barriers run on a host-side (gloo) group and do not wait for the attention kernels, which are
+still in flight when `forward` returns. No device-side code waits on a peer, and no load with
+cluster multicast is involved anywhere.
 
 The reference project is single-GPU (no ring, no LSE); this is an addition on top of its
 operator. `ring_schedule` / `chain_flags` are plain Python and tested on CPU.
@@ -52,33 +57,73 @@ class RingAttention:
     """Ring attention for fixed shard shapes. Collective: construct and call on every rank.
 
     k_local, v_local: this rank's shard [B, H, Lk_shard, 128] bf16 contiguous ('bhld'); all
-    ranks must use the same shard shape. q: [B, H, Lq_local, 128]. The K/V tensors must stay
-    alive and unmodified from `bind` until the matching `forward` has returned.
+    ranks must use the same shard shape. q: [B, H, Lq_local, 128]. The contents of a shard may
+    change between two `forward` calls (same tensors or new ones); they must not change while a
+    call is in progress. The results are produced asynchronously on the current stream: call
+    `synchronize()` (or synchronise the stream and `_native.device_check()`) before reading them
+    on the host.
     """
 
-    def __init__(self, group=None):
+    def __init__(self, group=None, native=None):
+        """`native` replaces the ctypes binding module (tests of the host logic pass a stand-in
+        whose IPC calls can be made to fail)."""
         import torch.distributed as dist
 
+        if native is None:
+            from . import _native as native
+            self._require_cuda = True
+        else:
+            self._require_cuda = False
+        self._native = native
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
+        # Host-only meeting point: a barrier on the NCCL group would queue behind the kernels.
+        ranks = dist.get_process_group_ranks(group) if group is not None else None
+        self._host_group = dist.new_group(ranks=ranks, backend="gloo") if self.world > 1 else None
         self._peers: List[Optional[_Peer]] = []
-        self._bound_shape = None
+        self._bound = None
+        self._keep = None
         self._staging = None
         self._partial = None
+        self._out = None
         self._copy_stream = None
+        self._events = None
+        self._ready = None
 
-    # -- peer mapping ----------------------------------------------------------------------
-    def bind(self, k_local, v_local) -> None:
-        """Exchange IPC handles of this call's K/V shards and map every peer's shard."""
+    def _meet(self) -> None:
+        import torch.distributed as dist
+
+        if self._host_group is not None:
+            dist.barrier(group=self._host_group)
+
+    def _any_rank(self, flag: bool) -> bool:
+        """True on every rank if `flag` is set on any rank (also a meeting point of all ranks)."""
         import torch
         import torch.distributed as dist
 
-        from . import _native as N
+        if self._host_group is None:
+            return flag
+        t = torch.tensor([int(flag)], dtype=torch.int32)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self._host_group)
+        return bool(t.item())
 
+    # -- peer mapping ----------------------------------------------------------------------
+    def bind(self, k_local, v_local) -> None:
+        """Exchange IPC handles of this call's K/V shards and map every peer's shard. Raises on
+        every rank if the shard shapes differ. (No ordering guarantee by itself: `forward` does
+        the waiting.)"""
+        import torch
+        import torch.distributed as dist
+
+        N = self._native
         lib = N.lib()
-        if not (k_local.is_cuda and v_local.is_cuda and k_local.is_contiguous() and v_local.is_contiguous()):
-            raise RuntimeError("ring shards must be contiguous CUDA tensors")
+        if self._require_cuda and not (k_local.is_cuda and v_local.is_cuda):
+            raise RuntimeError("ring shards must be CUDA tensors")
+        if not (k_local.is_contiguous() and v_local.is_contiguous()):
+            raise RuntimeError("ring shards must be contiguous")
+        if tuple(k_local.shape) != tuple(v_local.shape):
+            raise RuntimeError("k and v shards must have the same shape")
         self.unbind()
         mine = []
         for t in (k_local, v_local):
@@ -88,52 +133,64 @@ class RingAttention:
             mine.append((handle.raw, int(off.value)))
         info = {"shape": tuple(k_local.shape), "handles": mine}
         gathered = [None] * self.world
-        dist.all_gather_object(gathered, info, group=self.group)
+        dist.all_gather_object(gathered, info, group=self._host_group if self._host_group is not None else self.group)
         for g in gathered:
             if g["shape"] != info["shape"]:
                 raise RuntimeError(f"ring shards differ in shape: {g['shape']} vs {info['shape']}")
         self._peers = []
-        for r, g in enumerate(gathered):
-            if r == self.rank:
-                self._peers.append(_Peer(k_local.data_ptr(), v_local.data_ptr(), []))
-                continue
-            ptrs, bases = [], []
-            for raw, off in g["handles"]:
-                base = C.c_void_p()
-                N.check(lib.b200attn_ipc_open(raw, C.byref(base)))
-                bases.append(base.value)
-                ptrs.append(base.value + off)
-            self._peers.append(_Peer(ptrs[0], ptrs[1], bases))
-        self._bound_shape = tuple(k_local.shape)
+        try:
+            for r, g in enumerate(gathered):
+                if r == self.rank:
+                    self._peers.append(_Peer(k_local.data_ptr(), v_local.data_ptr(), []))
+                    continue
+                peer = _Peer(0, 0, [])
+                self._peers.append(peer)
+                ptrs = []
+                for raw, off in g["handles"]:
+                    base = C.c_void_p()
+                    N.check(lib.b200attn_ipc_open(raw, C.byref(base)))
+                    peer.mapped.append(base.value)
+                    ptrs.append(base.value + off)
+                peer.k_ptr, peer.v_ptr = ptrs
+        except Exception:
+            self.unbind()  # close what was mapped before the failure
+            raise
+        self._bound = (tuple(k_local.shape), k_local.data_ptr(), v_local.data_ptr())
         self._keep = (k_local, v_local)
-        if self._staging is None or tuple(self._staging[0][0].shape) != self._bound_shape:
+        if self._staging is None or tuple(self._staging[0][0].shape) != tuple(k_local.shape) \
+                or self._staging[0][0].device != k_local.device:
             self._staging = [tuple(torch.empty_like(k_local) for _ in range(2)) for _ in range(2)]
-        if self._copy_stream is None:
+        if self._copy_stream is None and k_local.is_cuda:
             self._copy_stream = torch.cuda.Stream(device=k_local.device)
-        dist.barrier(group=self.group)  # every shard is final and mapped before anybody pulls
 
     def unbind(self) -> None:
-        from . import _native as N
-
+        N = self._native
         for peer in self._peers:
             if peer is None:
                 continue
             for base in peer.mapped:
                 N.lib().b200attn_ipc_close(C.c_void_p(base))
+            peer.mapped = []
         self._peers = []
+        self._bound = None
         self._keep = None
 
-    # -- the ring ----------------------------------------------------------------------------
-    def forward(self, q, k_local, v_local, *, softmax_scale: float = 0.0, return_lse: bool = True):
+    def synchronize(self) -> None:
+        """Wait for the kernels of the calls made so far and report a device-side wait that ran out."""
         import torch
-        import torch.distributed as dist
 
-        from . import _native as N
+        torch.cuda.current_stream().synchronize()
+        self._native.device_check()
+
+    # -- the ring ----------------------------------------------------------------------------
+    def forward(self, q, k_local, v_local, *, softmax_scale: float = 0.0, return_lse: bool = True,
+                out=None):
+        import torch
+
         from . import ops
 
-        if not self._peers or self._bound_shape != tuple(k_local.shape) or \
-                self._peers[self.rank].k_ptr != k_local.data_ptr():
-            self.bind(k_local, v_local)
+        N = self._native
+        key = (tuple(k_local.shape), k_local.data_ptr(), v_local.data_ptr())
         lib = N.lib()
         dev = q.device
         B, H, Lq, D = q.shape
@@ -141,14 +198,29 @@ class RingAttention:
         if self._partial is None or tuple(self._partial[0].shape) != (B, H, Lq, D):
             self._partial = (torch.empty(B, H, Lq, D, dtype=torch.float32, device=dev),
                              torch.empty(B, H, Lq, dtype=torch.float32, device=dev))
+        if out is None:
+            if self._out is None or self._out.shape != q.shape or self._out.device != dev:
+                self._out = torch.empty_like(q)
+            out = self._out
         main = torch.cuda.current_stream(dev)
         side = self._copy_stream
         order = ring_schedule(self.world, self.rank)
         flags = chain_flags(self.world)
-        copied = [torch.cuda.Event() for _ in range(self.world)]
-        consumed = [torch.cuda.Event() for _ in range(self.world)]
-        out = torch.empty_like(q)
+        if self._events is None or len(self._events[0]) != self.world:
+            self._events = ([torch.cuda.Event() for _ in range(self.world)],
+                            [torch.cuda.Event() for _ in range(self.world)])
+            self._ready = torch.cuda.Event()
+        copied, consumed = self._events
         result = None
+
+        # Entry: whatever wrote this rank's K/V (on the current stream) has finished, on every
+        # rank, before anybody pulls. The ranks also agree here on whether the shards have to be
+        # (re)mapped: binding is collective, so one rank whose shard moved makes all of them bind.
+        if self.world > 1:
+            self._ready.record(main)
+            self._ready.synchronize()
+            if self._any_rank(not self._peers or self._bound != key):
+                self.bind(k_local, v_local)
 
         def start_pull(step: int) -> None:
             buf = self._staging[step % 2]
@@ -175,7 +247,10 @@ class RingAttention:
             consumed[step].record(main)
             if step + 2 < self.world:
                 start_pull(step + 2)
-        main.synchronize()
-        N.device_check()
-        dist.barrier(group=self.group)  # nobody may touch its shard while a peer still reads it
+        # Exit: this rank's pulls have landed, on every rank, so every shard may change again.
+        # (The last pull waits for the kernel two steps before the end; the last kernels are still
+        # running when this returns.)
+        if self.world > 1:
+            side.synchronize()
+            self._meet()
         return (result[0], result[1]) if return_lse else result[0]

@@ -16,7 +16,7 @@ is `batch * N`. Rank 0 prints one JSON line.
                    (CUDA events on the launch stream) over the measured cuBLAS bf16 peak
     cpu_baseline   torch SDPA (math backend, fp32) on the host cores over a bounded sample of the
                    same workload; it is what the reference project checks its kernels against
-    k18_same_gpu   the reference project's final kernel, built unmodified into oracle/_ref/,
+    k18_same_gpu   the reference project's final kernel, built unmodified into baseline/_ref/,
                    timed on the same GPU and inputs (null when that library is absent)
 
 `--impl reference` times the CPU arm alone (rank 0 only) and prints the same line shape.
@@ -747,14 +747,12 @@ def run_strong(args, rank, local_rank, world):
 
 def time_k18(torch, q, k, v, layout, args):
     try:
-        from oracle import native_refs as R
+        from baseline import k18 as R
     except Exception:
         return None
     fn = None
-    if layout == "bhld" and R.k18_available():
-        fn = R.k18_bhld
-    elif layout == "bshd" and (R.REF_DIR / "libk18_bshd_ref.so").exists():
-        fn = R.k18_bshd
+    if R.available(layout):
+        fn = R.bhld if layout == "bhld" else R.bshd
     lq = q.shape[2] if layout == "bhld" else q.shape[1]
     lk = k.shape[2] if layout == "bhld" else k.shape[1]
     if fn is None or lq % 256 or lk % 128:

@@ -147,8 +147,10 @@ B200ATTN_API int b200attn_copy_async(void* dst_local, const void* src, uint64_t 
  *   - The first call on a device looks up the array's device address and sets kernel
  *     attributes; make that call before any stream capture.
  *   - All calls on a device share the array: calls whose kernels overlap on the GPU race.
- *   - A device-side wait that ran out is reported by the next call that finds the stream idle;
- *     kv_splits == 0 launches nothing and only performs that check (synchronise first). */
+ *   - A launching call (kv_splits >= 1) never queries, copies from or waits for the stream. A
+ *     device-side wait that ran out is reported by a kv_splits == 0 call, which launches nothing,
+ *     synchronises args->stream and reads the record back; it returns
+ *     B200ATTN_ERR_INVALID_ARGUMENT on a stream that is being captured. */
 #define B200ATTN_NOALLOC_MAX_ROWS 16384
 B200ATTN_API int b200attn_forward_kv_split_noalloc(const b200attn_forward_args* args, int32_t kv_splits);
 

@@ -1,10 +1,6 @@
 """ctypes access to what oracle/Makefile builds into oracle/_ref/. TEST INFRASTRUCTURE ONLY.
 
   libsdpa_ref.so       the plain-C restatement (oracle/sdpa_ref.c), a CPU checker
-  libk18_ref.so        the reference's final checkpoint kernel, compiled unmodified from the
-                       mounted reference tree (kernels/5_minor/18_tma_l2_promotion.cu), used only
-                       as a same-GPU timing / cross-check arm
-  libk18_bshd_ref.so   its direct-BSHD variant (kernels/variants/18_tma_l2_promotion_bshd.cu)
 
 Nothing here is imported by the b200_attention_b200 package.
 """
@@ -17,8 +13,6 @@ from pathlib import Path
 import torch
 
 REF_DIR = Path(__file__).resolve().parent / "_ref"
-K18_SYMBOL = "_Z28attention_tcgen05_v18_launchPK13__nv_bfloat16S1_S1_PS_iiiP11CUstream_st"
-K18_BSHD_SYMBOL = "_Z33attention_tcgen05_v18_bshd_launchPK13__nv_bfloat16S1_S1_PS_iiiiP11CUstream_st"
 
 _cache: dict = {}
 
@@ -57,44 +51,3 @@ def sdpa_c_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
     if rc != 0:
         raise RuntimeError(f"sdpa_ref_forward failed with {rc}")
     return o, lse
-
-
-def k18_available() -> bool:
-    return (REF_DIR / "libk18_ref.so").exists()
-
-
-def k18_bhld(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
-    """Reference kernel on contiguous CUDA bf16 [B, H, L, 128]; needs Lq % 256 == 0, Lk % 128 == 0
-    (kernels/5_minor/18_tma_l2_promotion.cu:1011-1015)."""
-    lib = _load("libk18_ref.so")
-    if lib is None:
-        raise RuntimeError("oracle/_ref/libk18_ref.so is missing")
-    fn = getattr(lib, K18_SYMBOL)
-    fn.argtypes = [C.c_void_p] * 4 + [C.c_int] * 3 + [C.c_void_p]
-    fn.restype = None
-    assert q.is_cuda and q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
-    B, H, Lq, _ = q.shape
-    Lk = k.shape[2]
-    assert Lq % 256 == 0 and Lk % 128 == 0
-    o = torch.empty_like(q)
-    fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), B * H, Lq, Lk,
-       torch.cuda.current_stream().cuda_stream)
-    return o
-
-
-def k18_bshd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
-    """Reference direct-BSHD kernel on contiguous CUDA bf16 [B, L, H, 128]."""
-    lib = _load("libk18_bshd_ref.so")
-    if lib is None:
-        raise RuntimeError("oracle/_ref/libk18_bshd_ref.so is missing")
-    fn = getattr(lib, K18_BSHD_SYMBOL)
-    fn.argtypes = [C.c_void_p] * 4 + [C.c_int] * 4 + [C.c_void_p]
-    fn.restype = None
-    assert q.is_cuda and q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
-    B, Lq, H, _ = q.shape
-    Lk = k.shape[1]
-    assert Lq % 256 == 0 and Lk % 128 == 0
-    o = torch.empty_like(q)
-    fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), B, H, Lq, Lk,
-       torch.cuda.current_stream().cuda_stream)
-    return o

@@ -72,6 +72,8 @@ def _args(**over):
     (dict(causal=1, len_q=512), N.STATUS_UNSUPPORTED),                           # len_kv < len_q
     (dict(causal=1, kernel=1), N.STATUS_UNSUPPORTED),                            # serial kernel
     (dict(heads=4, heads_kv=2, kernel=1), N.STATUS_UNSUPPORTED),
+    (dict(causal=1, partial_o=0x20000, partial_lse=0x30000, partial_emit=1), N.STATUS_UNSUPPORTED),
+    (dict(causal=1, partial_o=0x20000, partial_lse=0x30000, partial_merge=1), N.STATUS_UNSUPPORTED),
 ])
 def test_argument_errors_come_back_as_status_codes(native_built, over, status):
     a = _args(**over)
@@ -81,6 +83,28 @@ def test_argument_errors_come_back_as_status_codes(native_built, over, status):
     with pytest.raises(N.B200AttnError) as info:
         N.check(rc)
     assert info.value.status == status
+
+
+@pytest.mark.parametrize("over, splits, status", [
+    (dict(partial_o=0x20000, partial_lse=0x30000), 2, N.STATUS_INVALID_ARGUMENT),  # scratch is built in
+    (dict(partial_emit=1), 2, N.STATUS_INVALID_ARGUMENT),
+    (dict(causal=1), 2, N.STATUS_UNSUPPORTED),
+    (dict(heads=4, heads_kv=2), 2, N.STATUS_UNSUPPORTED),
+    (dict(kernel=1), 2, N.STATUS_INVALID_ARGUMENT),                                # serial kernel
+    (dict(len_q=N.NOALLOC_MAX_ROWS + 1), 2, N.STATUS_UNSUPPORTED),                 # beyond the array
+    (dict(batch=2, heads=64, len_q=256), 2, N.STATUS_UNSUPPORTED),                 # 32768 rows
+    (dict(), -1, N.STATUS_INVALID_ARGUMENT),
+    (dict(), 65, N.STATUS_INVALID_ARGUMENT),
+    (dict(head_dim=64), 1, N.STATUS_UNSUPPORTED),
+    (dict(q=N.Operand(0, 0, 256 * 128, 128)), 1, N.STATUS_INVALID_ARGUMENT),
+])
+def test_no_alloc_entry_rejects_before_touching_a_device(native_built, over, splits, status):
+    """Every argument rule of the allocation-free entry point is checked before its first CUDA
+    call, so the refusals can be seen without a GPU."""
+    a = _args(**over)
+    rc = N.lib().b200attn_forward_kv_split_noalloc(C.byref(a), splits)
+    assert rc == status
+    assert N.lib().b200attn_last_error() != b""
 
 
 def test_null_args(native_built):
@@ -116,3 +140,15 @@ def test_ops_refuse_cpu_tensors():
     x = torch.zeros(1, 1, 256, 128, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="no CPU path"):
         ops.attention(x, x, x)
+
+
+def test_reference_side_launcher_bindings_compile_and_link(native_built, tmp_path):
+    """The forwarding translation unit a maintainer of the reference adds (the C++ launcher
+    signatures of benchmarks/registry.py:272-282 and benchmarks/benchmark_bshd.py:151-160) builds
+    against libb200attn.so and exports both launchers under the names the reference's generated
+    glue would link."""
+    from tests.integration import build_forwarders as B
+
+    so = B.build(native_built["core"], tmp_path)
+    lib = C.CDLL(str(so))
+    assert hasattr(lib, B.BHLD_SYMBOL) and hasattr(lib, B.BSHD_SYMBOL)

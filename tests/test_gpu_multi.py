@@ -48,22 +48,29 @@ def _worker(rank: int, world: int, port: int, queue):
             good &= st["o_max_abs"] <= O.O_MAX_ABS and st["o_mean_abs"] <= O.O_MEAN_ABS and st["lse_max_abs"] <= O.LSE_MAX_ABS
         ok["shard"] = bool(good)
 
-        # ---- sequence-parallel ring, twice (the second call reuses mappings and buffers)
+        # ---- sequence-parallel ring: twice on the same shards (the second call reuses mappings
+        # and buffers), then once more after the shards were rewritten IN PLACE with other data
+        # (same addresses: nothing may be pulled before the owner's writes have landed)
         B, H, L = 1, 4, 512 * world
-        q, k, v = (O.to_bhld(t) for t in O.make_inputs_benchmark(B, H, L, L, seed=51))
-        o_ref, lse_ref = O.sdpa_explicit(q, k, v)
         n = L // world
         rows = slice(rank * n, (rank + 1) * n)
-        q_l = q[:, :, rows].contiguous().cuda()
-        k_l = k[:, :, rows].contiguous().cuda()
-        v_l = v[:, :, rows].contiguous().cuda()
         ra = ring.RingAttention()
         good = True
-        for _ in range(2):
-            o, lse = ra.forward(q_l, k_l, v_l)
-            st = O.compare(o.cpu(), o_ref[:, :, rows], lse.cpu(), lse_ref[:, :, rows])
-            good &= st["finite"] and st["o_max_abs"] <= O.O_MAX_ABS and st["o_mean_abs"] <= O.O_MEAN_ABS \
-                and st["lse_max_abs"] <= O.LSE_MAX_ABS
+        q_l = k_l = v_l = None
+        for seed, calls in ((51, 2), (52, 1)):
+            q, k, v = (O.to_bhld(t) for t in O.make_inputs_benchmark(B, H, L, L, seed=seed))
+            o_ref, lse_ref = O.sdpa_explicit(q, k, v)
+            if q_l is None:
+                q_l, k_l, v_l = (t[:, :, rows].contiguous().cuda() for t in (q, k, v))
+            else:
+                for dst, src in ((q_l, q), (k_l, k), (v_l, v)):
+                    dst.copy_(src[:, :, rows], non_blocking=True)
+            for _ in range(calls):
+                o, lse = ra.forward(q_l, k_l, v_l)
+                ra.synchronize()
+                st = O.compare(o.cpu(), o_ref[:, :, rows], lse.cpu(), lse_ref[:, :, rows])
+                good &= st["finite"] and st["o_max_abs"] <= O.O_MAX_ABS and st["o_mean_abs"] <= O.O_MEAN_ABS \
+                    and st["lse_max_abs"] <= O.LSE_MAX_ABS
         ra.unbind()
         ok["ring"] = bool(good)
         ok["ring_stats"] = st
@@ -77,7 +84,7 @@ def _worker(rank: int, world: int, port: int, queue):
             pass
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_sharding_and_ring_across_gpus(native_built, world):
     if not torch.cuda.is_available():
         pytest.fail("this test needs CUDA devices")

@@ -193,3 +193,64 @@ def test_calls_can_be_captured_in_a_cuda_graph(gpu):
     _native.device_check()
     ref, _ = O.sdpa_explicit(O.to_bhld(q.cpu()), O.to_bhld(k.cpu()), O.to_bhld(v.cpu()))
     O.assert_within_contract(O.compare(O.to_bhld(o_self.cpu()), ref))
+
+
+def _raw_launch_inputs(b, h, lq, lk, seed):
+    q, k, v = O.make_inputs_benchmark(b, h, lq, lk, seed=seed)  # BSHD on the host
+    o_ref, _ = O.sdpa_explicit(O.to_bhld(q), O.to_bhld(k), O.to_bhld(v))
+    return q, k, v, o_ref
+
+
+def test_launcher_symbols_on_raw_pointers(gpu):
+    """b200attn_bhld_launch / b200attn_bshd_launch, the replacements of the reference's two
+    launcher symbols, called through ctypes on bare device pointers."""
+    from b200_attention_b200 import _native as N
+
+    lib = N.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    b, h, lq, lk = 2, 3, 512, 640
+    q, k, v, o_ref = _raw_launch_inputs(b, h, lq, lk, seed=70)
+    # token-major in place
+    qs, ks, vs = q.cuda(), k.cuda(), v.cuda()
+    out_s = torch.empty_like(qs)
+    N.check(lib.b200attn_bshd_launch(qs.data_ptr(), ks.data_ptr(), vs.data_ptr(), out_s.data_ptr(),
+                                     b, h, lq, lk, stream))
+    # head-major, batch and heads flattened as the reference launcher takes them
+    qh, kh, vh = (O.to_bhld(t).cuda() for t in (q, k, v))
+    out_h = torch.empty_like(qh)
+    N.check(lib.b200attn_bhld_launch(qh.data_ptr(), kh.data_ptr(), vh.data_ptr(), out_h.data_ptr(),
+                                     b * h, lq, lk, stream))
+    torch.cuda.synchronize()
+    N.device_check()
+    O.assert_within_contract(O.compare(O.to_bhld(out_s.cpu()), o_ref))
+    O.assert_within_contract(O.compare(out_h.cpu(), o_ref))
+    assert torch.equal(out_s.transpose(1, 2), out_h)
+
+
+def test_reference_side_launcher_bindings_run(gpu, tmp_path):
+    """The forwarding translation unit with the reference's C++ launcher signatures, compiled and
+    called by mangled name exactly as the reference's own final kernel is called in
+    baseline/k18.py."""
+    import ctypes as C
+
+    from b200_attention_b200 import _native as N
+    from tests.integration import build_forwarders as B
+
+    fwd = C.CDLL(str(B.build(gpu["core"], tmp_path)))
+    bhld = getattr(fwd, B.BHLD_SYMBOL)
+    bhld.argtypes, bhld.restype = [C.c_void_p] * 4 + [C.c_int] * 3 + [C.c_void_p], None
+    bshd = getattr(fwd, B.BSHD_SYMBOL)
+    bshd.argtypes, bshd.restype = [C.c_void_p] * 4 + [C.c_int] * 4 + [C.c_void_p], None
+    stream = torch.cuda.current_stream().cuda_stream
+    b, h, lq, lk = 1, 4, 768, 384  # the reference's own shape rule holds: Lq % 256 == 0, Lk % 128 == 0
+    q, k, v, o_ref = _raw_launch_inputs(b, h, lq, lk, seed=71)
+    qh, kh, vh = (O.to_bhld(t).cuda() for t in (q, k, v))
+    out_h = torch.empty_like(qh)
+    bhld(qh.data_ptr(), kh.data_ptr(), vh.data_ptr(), out_h.data_ptr(), b * h, lq, lk, stream)
+    qs, ks, vs = q.cuda(), k.cuda(), v.cuda()
+    out_s = torch.empty_like(qs)
+    bshd(qs.data_ptr(), ks.data_ptr(), vs.data_ptr(), out_s.data_ptr(), b, h, lq, lk, stream)
+    torch.cuda.synchronize()
+    N.device_check()
+    O.assert_within_contract(O.compare(out_h.cpu(), o_ref))
+    O.assert_within_contract(O.compare(O.to_bhld(out_s.cpu()), o_ref))

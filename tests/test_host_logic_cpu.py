@@ -193,3 +193,104 @@ def test_two_rank_gloo_sharding_and_ring():
         p.join(timeout=120)
         assert p.exitcode == 0
     assert queue.get(timeout=10) == [1, 1]
+
+
+# ------------------------------------------------- ring host failure paths, gloo, world size 2
+class _FakeNative:
+    """Stand-in for the ctypes binding: IPC export/open/close without a GPU. `fail_open_on` makes
+    b200attn_ipc_open return a non-zero status on that rank, after `fail_after` successful opens."""
+
+    STATUS_CUDA = 4
+
+    class Error(RuntimeError):
+        def __init__(self, status):
+            super().__init__(f"status {status}")
+            self.status = status
+
+    def __init__(self, rank, fail_open_on=None, fail_after=0):
+        self.rank, self.fail_open_on, self.fail_after = rank, fail_open_on, fail_after
+        self.opened, self.closed = [], []
+
+    def lib(self):
+        return self
+
+    def check(self, status):
+        if status != 0:
+            raise _FakeNative.Error(status)
+
+    def b200attn_ipc_export(self, ptr, handle, off):
+        import ctypes as C
+
+        C.memmove(handle, int(ptr).to_bytes(8, "little") * 8, 64)
+        off._obj.value = 0
+        return 0
+
+    def b200attn_ipc_open(self, raw, base):
+        if self.fail_open_on == self.rank and len(self.opened) >= self.fail_after:
+            return self.STATUS_CUDA
+        value = int.from_bytes(raw[:8], "little")
+        base._obj.value = value
+        self.opened.append(value)
+        return 0
+
+    def b200attn_ipc_close(self, base):
+        self.closed.append(base.value)
+        return 0
+
+
+def _ring_failure_worker(rank: int, world: int, port: int, result_queue):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    out = {}
+    try:
+        # 1. shards of different shapes: every rank raises, nothing stays mapped
+        fake = _FakeNative(rank)
+        ra = ring.RingAttention(native=fake)
+        shard = torch.zeros(1, 2, 128 * (rank + 1), 128, dtype=torch.bfloat16)
+        try:
+            ra.bind(shard, shard.clone())
+            out["mismatch"] = "no error"
+        except RuntimeError as exc:
+            out["mismatch"] = "differ in shape" in str(exc)
+        out["mismatch_clean"] = ra._peers == [] and fake.opened == []
+
+        # 2. the second IPC open fails on rank 1: it surfaces as the status, and what had been
+        #    opened before is closed again; rank 0 binds normally and unbinds normally
+        fake = _FakeNative(rank, fail_open_on=1, fail_after=1)
+        ra = ring.RingAttention(native=fake)
+        k, v = torch.zeros(1, 2, 128, 128, dtype=torch.bfloat16), torch.zeros(1, 2, 128, 128, dtype=torch.bfloat16)
+        try:
+            ra.bind(k, v)
+            out["open"] = "bound"
+            ra.unbind()
+        except _FakeNative.Error as exc:
+            out["open"] = exc.status
+        out["open_clean"] = sorted(fake.opened) == sorted(fake.closed) and ra._peers == []
+        out["opened"] = len(fake.opened)
+    except Exception as exc:
+        out["error"] = repr(exc)
+    finally:
+        result_queue.put((rank, out))
+        dist.destroy_process_group()
+
+
+def test_two_rank_gloo_ring_failure_paths():
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ring_failure_worker, args=(r, 2, port, queue)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(queue.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank in (0, 1):
+        assert "error" not in results[rank], results[rank]
+        assert results[rank]["mismatch"] is True and results[rank]["mismatch_clean"], results[rank]
+        assert results[rank]["open_clean"], results[rank]
+    assert results[0]["open"] == "bound" and results[0]["opened"] == 2
+    assert results[1]["open"] == _FakeNative.STATUS_CUDA and results[1]["opened"] == 1
