@@ -38,6 +38,7 @@ EXPORTED_SYMBOLS = (
     "b200attn_device_check",
     "b200attn_set_wait_limit_ms",
     "b200attn_launch_count",
+    "b200attn_sample_sm_clocks",
     "b200attn_ipc_export",
     "b200attn_ipc_open",
     "b200attn_ipc_close",
@@ -115,6 +116,8 @@ def lib() -> C.CDLL:
         handle.b200attn_set_wait_limit_ms.restype = C.c_int
         handle.b200attn_launch_count.argtypes = []
         handle.b200attn_launch_count.restype = C.c_uint64
+        handle.b200attn_sample_sm_clocks.argtypes = [C.c_void_p, C.c_int32, C.c_void_p]
+        handle.b200attn_sample_sm_clocks.restype = C.c_int
         handle.b200attn_ipc_export.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64)]
         handle.b200attn_ipc_export.restype = C.c_int
         handle.b200attn_ipc_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]

@@ -109,7 +109,6 @@ struct WaitCtx {
   uint64_t limit_ns;
   int32_t item;
   int32_t tile;
-  bool single_issuer = false;  // wait_issue() is called by one thread, not by a converged warp
 
   __device__ __forceinline__ bool aborted() const {
     uint32_t v;
@@ -152,7 +151,7 @@ struct WaitCtx {
 
   // For the MMA and TMA roles, which whole warps run with uniform control flow.
   __device__ __forceinline__ bool wait_issue(uint32_t bar, uint32_t parity, int site) const {
-    return single_issuer ? wait(bar, parity, site) : wait_warp(bar, parity, site);
+    return wait_warp(bar, parity, site);
   }
 
   // For roles run by whole warps: every lane returns the same answer, so the warp stays
@@ -320,11 +319,6 @@ __device__ __forceinline__ float row_max(const uint32_t (&s)[4][32]) {
 // ==========================================================================================
 // Warp-specialised persistent kernel
 // ==========================================================================================
-// Of every 16 exponentials, this many are computed with the FMA-pipe polynomial instead of the
-// MUFU unit (even numbers, 0..8).
-#ifndef B200ATTN_POLY_PER_16
-#define B200ATTN_POLY_PER_16 0
-#endif
 // A row keeps its reference maximum m until some score exceeds m by this many log2 units.
 // With bf16 probabilities and fp32 sums nothing overflows or loses relative precision until the
 // excess nears 2^100, so the bound can be generous; 32 makes a rebase a once-in-a-blue-moon event
@@ -332,46 +326,13 @@ __device__ __forceinline__ float row_max(const uint32_t (&s)[4][32]) {
 #ifndef B200ATTN_REBASE_LOG2
 #define B200ATTN_REBASE_LOG2 32.0f
 #endif
-// Where the bf16 probabilities of a tile go. 1: into columns 64..127 of the tile's S, each
-// 32-key chunk stored as soon as it has been computed (scores 64..127 are taken first, from
-// registers, so scores 0..63 stay intact in TMEM for the rare exact path). 0: into columns 0..63,
-// all four chunks stored after the last exponential.
-#ifndef B200ATTN_P_HIGH
-#define B200ATTN_P_HIGH 0
-#endif
-// The two Q tiles of a CTA run the same chain (scores -> softmax -> PV -> next scores) and share
-// one MUFU unit per sub-partition and one tensor pipe. Their phase offset is whatever the start of
-// an item leaves behind: with both first score tiles issued back to back it settles at the
-// minimum the tensor pipe allows (one Q tile's PV + QK), where the two softmax phases overlap.
-// Holding the second Q tile's first scores back by this many cycles at the start of an item (if
-// the item has at least kStaggerMinTiles tiles) moves the two chains towards opposite phase.
-#ifndef B200ATTN_STAGGER
-#define B200ATTN_STAGGER 0
-#endif
-constexpr int kStaggerCycles = B200ATTN_STAGGER;
-constexpr int kStaggerMinTiles = 12;
-constexpr int kPOffset = B200ATTN_P_HIGH ? 64 : 0;  // TMEM column of P inside its S
 
 constexpr int kPairSlots = 2;                 // ring of (V, K) pairs
 constexpr int kPairBytes = 2 * kTileBytes;    // V tile, then K tile
 constexpr int kWsThreads = 512;
-#ifndef B200ATTN_REGS_SOFTMAX
-#define B200ATTN_REGS_SOFTMAX 192
-#endif
-#ifndef B200ATTN_REGS_EPILOGUE
-#define B200ATTN_REGS_EPILOGUE 80
-#endif
-#ifndef B200ATTN_REGS_OTHER
-#define B200ATTN_REGS_OTHER 48
-#endif
-constexpr int kRegsSoftmax = B200ATTN_REGS_SOFTMAX;
-constexpr int kRegsEpilogue = B200ATTN_REGS_EPILOGUE;
-constexpr int kRegsOther = B200ATTN_REGS_OTHER;
-// 1: the MMA role is run by one elected thread of its warp (plain spins, unpredicated issue)
-// instead of by the whole warp with uniform operands and one lane predicated on.
-#ifndef B200ATTN_MMA_SINGLE
-#define B200ATTN_MMA_SINGLE 0
-#endif
+constexpr int kRegsSoftmax = 192;
+constexpr int kRegsEpilogue = 80;
+constexpr int kRegsOther = 48;
 
 enum WsBarrier : int {
   kBarQFull = 0,    // +q   TMA -> MMA       Q tile q landed
@@ -620,7 +581,7 @@ __device__ void ws_mma_role_causal(const FwdParams& p, uint32_t smem_q, uint32_t
           }
           if (!(ok = w.wait_issue(bar(kBarPReady + q), p_parity[q], 220 + q))) break;
           tc_fence_after_sync();
-          issue_pv(lead, o_tmem, s_tmem + kPOffset, v_smem, /*accumulate=*/i > 0);
+          issue_pv(lead, o_tmem, s_tmem, v_smem, /*accumulate=*/i > 0);
           p_parity[q] ^= 1u;
           if (i + 1 < Tq[q]) {
             issue_qk(lead, s_tmem, smem_q + q * kTileBytes, k_smem);
@@ -688,10 +649,6 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
       issue_qk(lead, tmem_base + q * kBlockN, smem_q + q * kTileBytes, k_smem);
       umma_commit_lead(lead, bar(kBarSFull + q));
       if (T == 1) umma_commit_lead(lead, bar(kBarQEmpty + q));
-      if (kStaggerCycles > 0 && q == 0 && T >= kStaggerMinTiles) {
-        const uint32_t t0 = uint32_t(clock());
-        while (uint32_t(clock()) - t0 < uint32_t(kStaggerCycles)) { }
-      }
     }
     }
     if (!ok) break;
@@ -725,7 +682,7 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
         tc_fence_after_sync();
         PROF_LAP(3);
         if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 1);
-        issue_pv(lead, o_tmem, s_tmem + kPOffset, v_smem, /*accumulate=*/i > 0);
+        issue_pv(lead, o_tmem, s_tmem, v_smem, /*accumulate=*/i > 0);
         PROF_LAP(4);
         if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 2);
         if (!has_next) {
@@ -760,65 +717,21 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
   }
 }
 
-// Which of the 16 column pairs of a 32-column chunk take the FMA-pipe polynomial instead of the
-// MUFU unit: B200ATTN_POLY_PER_16 / 2 of every 8 pairs, spread evenly so that MUFU and FMA work
-// alternate inside the instruction stream rather than coming in blocks.
-__device__ __forceinline__ constexpr bool use_poly(int j) {
-  constexpr int kPerEight = B200ATTN_POLY_PER_16 / 2;
-  const int k = j & 7;
-  return ((k + 1) * kPerEight) / 8 != (k * kPerEight) / 8;
-}
-
 // ---- softmax: one query row per thread ---------------------------------------------------
-// Per-row constants of the exponential: 2^(s * c - m) with c = softmax scale * log2(e) and m the
-// row's reference maximum, which is kept INTEGER-valued (any reference works; an integer one lets
-// the polynomial path get floor(s * c - m) out of a single fused multiply-add).
-struct ExpRow {
-  f2 scale2;   // (c, c)
-  f2 neg_m2;   // (-m, -m)                      MUFU path
-  f2 magic2;   // (1.5 * 2^23 - m) twice        polynomial path
-  float s_lo;  // raw scores below this are clamped: keeps s * c - m >= -125 for the polynomial
-};
-
-__device__ __forceinline__ ExpRow make_exp_row(float scale_log2, float m) {
-  ExpRow e;
-  e.scale2 = f2_splat(scale_log2);
-  e.neg_m2 = f2_splat(-m);
-  e.magic2 = f2_splat(12582912.0f - m);
-  e.s_lo = (m - 125.0f) / scale_log2;
-  return e;
-}
-
 // 2^(s * c - m) for one 32-column chunk: 16 packed bf16 pairs out, row-sum pairs accumulated.
-// `poly_hi` collects the maximum raw score that went through the polynomial, whose result is only
-// meaningful up to s * c - m = 128 (beyond that the exponent field wraps): the caller checks it.
-template <bool kAllowPoly>
-__device__ __forceinline__ void exp_chunk(const uint32_t (&s)[32], const ExpRow& e,
-                                          uint32_t (&packed)[16], f2& sum_a, f2& sum_b,
-                                          float& poly_hi) {
+__device__ __forceinline__ void exp_chunk(const uint32_t (&s)[32], f2 scale2, f2 neg_m2,
+                                          uint32_t (&packed)[16], f2& sum_a, f2& sum_b) {
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
-    const float s0 = __uint_as_float(s[2 * j]), s1 = __uint_as_float(s[2 * j + 1]);
-    f2 r;
-    if (kAllowPoly && use_poly(j)) {
-      poly_hi = max3(poly_hi, s0, s1);
-      r = exp2_poly_scaled(f2_make(fmaxf(s0, e.s_lo), fmaxf(s1, e.s_lo)), e.scale2, e.magic2);
-    } else {
-      const f2 x = f2_fma(f2_make(s0, s1), e.scale2, e.neg_m2);
-      float x0, x1;
-      f2_split(x, x0, x1);
-      r = f2_make(ex2_approx(x0), ex2_approx(x1));
-    }
-    if (j & 1) sum_b = f2_add(sum_b, r); else sum_a = f2_add(sum_a, r);
-    float e0, e1;
-    f2_split(r, e0, e1);
+    const f2 x = f2_fma(f2_make(__uint_as_float(s[2 * j]), __uint_as_float(s[2 * j + 1])), scale2,
+                        neg_m2);
+    float x0, x1;
+    f2_split(x, x0, x1);
+    const float e0 = ex2_approx(x0), e1 = ex2_approx(x1);
+    const f2 e = f2_make(e0, e1);
+    if (j & 1) sum_b = f2_add(sum_b, e); else sum_a = f2_add(sum_a, e);
     packed[j] = pack_bf16x2(e0, e1);
   }
-}
-
-// The n-th 32-key chunk of a tile the softmax visits (see kPOffset).
-__device__ __forceinline__ constexpr int chunk_at(int n) {
-  return B200ATTN_P_HIGH ? ((n + 2) & 3) : n;
 }
 
 __device__ __forceinline__ float f2_hsum(f2 a, f2 b) {
@@ -832,32 +745,28 @@ __device__ __forceinline__ float f2_hsum(f2 a, f2 b) {
 //
 // Tiles after the first do not start with a row-maximum pass. The tile is exponentiated
 // speculatively against the current m; the speculation holds if the row's sum of the tile stays
-// below 2^kRebase (then no single probability reached 2^kRebase) and no score that took the
-// polynomial path lies above m + kRebase. Otherwise, and always on the first tile, the warp takes
-// the exact path: fetch the scores again where their registers were consumed, take the true
-// maximum, move m (rounded up to an integer), multiply l and the row's O accumulator in TMEM by
-// 2^(m_old - m_new) (O is stable here: the scores of this tile exist, so the previous PV has
-// finished, and the next PV has not been released yet), and redo the tile with every exponential
-// on the MUFU unit. P_READY is signalled only after the decision, so although chunks of P may
-// already sit in TMEM there is never anything to retract.
-//
-// The 32-key chunks are visited in the order chunk_at(0..3). With P in the upper half of S the
-// chunks whose scores the P stores overwrite (64..127) go first, out of registers; scores 0..63
-// stay intact in TMEM.
+// below 2^kRebase (then no single probability reached 2^kRebase). Otherwise, and always on the
+// first tile, the warp takes the exact path: fetch the scores again (S is still intact in TMEM,
+// nothing has been stored over it yet), take the true maximum, move m, multiply l and the row's
+// O accumulator in TMEM by 2^(m_old - m_new) (O is stable here: the scores of this tile exist, so
+// the previous PV has finished, and the next PV has not been released yet), and redo the tile.
+// P is stored and P_READY signalled only after the decision, so there is never anything to
+// retract. All exponentials run on the MUFU unit and P is handed over in one piece: handing the
+// first columns over early, an FMA-pipe polynomial for part of the exponentials, and storing P
+// chunk by chunk as it is produced each measured slower in this kernel.
 template <bool kCausal>
 __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, uint32_t tmem_base,
                                 int q, int warp_in_group, int lane, WaitCtx& w) {
   auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
   constexpr float kRebase = B200ATTN_REBASE_LOG2;
-  constexpr bool kPHigh = B200ATTN_P_HIGH != 0;
-  constexpr bool kPoly = B200ATTN_POLY_PER_16 != 0;
   const float sum_limit = exp2f(kRebase);
   const uint32_t lane_field = uint32_t(warp_in_group * 32) << 16;
   const uint32_t s_tmem = tmem_base + q * kBlockN + lane_field;
-  const uint32_t p_tmem = s_tmem + kPOffset;  // bf16 P: 64 columns inside its S
+  const uint32_t p_tmem = s_tmem;  // bf16 P overwrites S columns 0..63
   const uint32_t o_tmem = tmem_base + kQTilesPerItem * kBlockN + q * kHeadDim + lane_field;
   const int r = warp_in_group * 32 + lane;
   const float scale_log2 = p.scale_log2;
+  const f2 scale2 = f2_splat(scale_log2);
   const int last_tile = p.kv_tiles - 1;
   const int tail_valid = p.len_kv - last_tile * kBlockN;  // keys in the last tile, 1..128
 #ifdef B200ATTN_TRACE
@@ -879,9 +788,8 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
     // the previous item's last PV has finished, which is what the epilogue waits for.
     if (!w.wait_warp(bar(kBarFinFree + q), fin_free_parity, 310 + q)) return;
     fin_free_parity ^= 1u;
-    float m = kNegInf;  // reference maximum, log2 units, integer-valued once set
+    float m = kNegInf;  // reference maximum, log2 units
     float l = 0.0f;     // running sum of 2^(s - m)
-    ExpRow er = make_exp_row(scale_log2, 0.0f);
     // causal: this row sees keys 0 .. row + causal_off; its Q tile's first row sees the fewest
     const int row0 = kCausal ? decode_item<true>(p, item).row0 : 0;
     const int T = q_tile_tiles<kCausal>(p, row0, q);
@@ -898,11 +806,11 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
       if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 1);
 
       uint32_t s[4][32];
-      tmem_ld32(s_tmem + chunk_at(0) * 32, s[chunk_at(0)]);
-      tmem_wait_ld();  // the first chunk alone, so that its exponentials overlap the other loads
-      tmem_ld32(s_tmem + chunk_at(1) * 32, s[chunk_at(1)]);
-      tmem_ld32(s_tmem + chunk_at(2) * 32, s[chunk_at(2)]);
-      tmem_ld32(s_tmem + chunk_at(3) * 32, s[chunk_at(3)]);
+      tmem_ld32(s_tmem + 0, s[0]);
+      tmem_wait_ld();  // chunk 0 alone, so that its exponentials overlap the other three loads
+      tmem_ld32(s_tmem + 32, s[1]);
+      tmem_ld32(s_tmem + 64, s[2]);
+      tmem_ld32(s_tmem + 96, s[3]);
       PROF_LAP(2);
       if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 2);
       // keys of this tile that exist for this row: all 128, fewer in a ragged last tile, and with
@@ -916,48 +824,31 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
       if (tail || i == 0) tmem_wait_ld();  // these paths look at all chunks at once
       if (tail) mask_tail(s, valid);
 
-      uint32_t packed[kPHigh ? 1 : 4][16];
+      uint32_t packed[4][16];
       f2 sum_a = f2_splat(0.0f), sum_b = f2_splat(0.0f);
       float tile_sum = 0.0f;
       bool exact = (i == 0);
       if (!exact) {
-        float poly_hi = kNegInf;
+        const f2 neg_m2 = f2_splat(-m);
 #pragma unroll
-        for (int n = 0; n < 4; ++n) {
-          const int c = chunk_at(n);
-#ifdef B200ATTN_NO_EXP  // timing study only: no exponentials, P is garbage
-          for (int j = 0; j < 16; ++j) packed[kPHigh ? 0 : c][j] = s[c][2 * j] & 0x3f003f00u;
-#else
-          exp_chunk<kPoly>(s[c], er, packed[kPHigh ? 0 : c], sum_a, sum_b, poly_hi);
-#endif
-          if (n == 0) tmem_wait_ld();  // every score is in registers from here on
-          if (kPHigh) tmem_st16(p_tmem + c * 16, packed[0]);
+        for (int c = 0; c < 4; ++c) {
+          exp_chunk(s[c], scale2, neg_m2, packed[c], sum_a, sum_b);
+          if (c == 0) tmem_wait_ld();
         }
         tile_sum = f2_hsum(sum_a, sum_b);
         // written so that a NaN sum also lands on the exact path
-        bool bad = !(tile_sum < sum_limit);
-        if (kPoly) bad = bad || (fmaf(poly_hi, scale_log2, -m) > kRebase);
-        exact = __any_sync(0xffffffffu, bad);
+        exact = __any_sync(0xffffffffu, !(tile_sum < sum_limit));
       }
       if (tr) B200ATTN_TRACE_EVENT_AFTER(p, q, item, i, 0, 6, tile_sum);
       if (__builtin_expect(exact, 0)) {
         if (i > 0) {
-          // Scores whose registers the speculation consumed or whose TMEM columns no P store has
-          // touched are fetched again (with P in the upper half that is chunks 0 and 1; chunks 2
-          // and 3 are still in their registers. With P in the lower half nothing has been stored
-          // yet and all of S is intact).
-          if (kPHigh) {
-            tmem_wait_st();
-            tmem_ld32(s_tmem + 0, s[0]);
-            tmem_ld32(s_tmem + 32, s[1]);
-          } else {
+          // the score registers were consumed by the speculation: fetch them again
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, s[c]);
-          }
+          for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, s[c]);
           tmem_wait_ld();
           if (tail) mask_tail(s, valid);
         }
-        const float tile_max = ceilf(row_max(s) * scale_log2);
+        const float tile_max = row_max(s) * scale_log2;
         if (i == 0) {
           m = tile_max;
         } else {
@@ -978,28 +869,21 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
             tmem_wait_st();
           }
         }
-        er = make_exp_row(scale_log2, m);
+        const f2 neg_m2 = f2_splat(-m);
         sum_a = f2_splat(0.0f);
         sum_b = f2_splat(0.0f);
-        float unused = kNegInf;
 #pragma unroll
-        for (int n = 0; n < 4; ++n) {
-          const int c = chunk_at(n);
-          exp_chunk<false>(s[c], er, packed[kPHigh ? 0 : c], sum_a, sum_b, unused);
-          if (kPHigh) tmem_st16(p_tmem + c * 16, packed[0]);
-        }
+        for (int c = 0; c < 4; ++c) exp_chunk(s[c], scale2, neg_m2, packed[c], sum_a, sum_b);
         tile_sum = f2_hsum(sum_a, sum_b);
       }
       if (tr) B200ATTN_TRACE_EVENT_AFTER(p, q, item, i, 0, 3, tile_sum);
 #ifdef B200ATTN_PROFILE
-      asm volatile("" ::"f"(tile_sum), "r"(packed[0][15]));
+      asm volatile("" ::"f"(tile_sum), "r"(packed[3][15]));
 #endif
       PROF_LAP(3);
 
-      if (!kPHigh) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_st16(p_tmem + c * 16, packed[c]);
-      }
+      for (int c = 0; c < 4; ++c) tmem_st16(p_tmem + c * 16, packed[c]);
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
@@ -1122,14 +1006,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
     reg_shrink<kRegsOther>();
     const uint32_t lead = (lane == 0) ? 1u : 0u;
     if (warp == 12) {
-      if (B200ATTN_MMA_SINGLE && !kCausal) {
-        if (elect_one()) {
-          w.single_issuer = true;
-          ws_mma_role<kCausal>(p, smem_q, smem_kv, bar0, tmem_base, 1u, w);
-        }
-      } else {
-        ws_mma_role<kCausal>(p, smem_q, smem_kv, bar0, tmem_base, lead, w);
-      }
+      ws_mma_role<kCausal>(p, smem_q, smem_kv, bar0, tmem_base, lead, w);
     } else if (warp == 13) {
       if (lead) {
         tma_prefetch_desc(&tmap_q);

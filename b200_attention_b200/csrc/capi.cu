@@ -209,6 +209,18 @@ int check_operand(const char* name, const b200attn_operand& t, int32_t batch, in
 }  // namespace host
 }  // namespace b200attn
 
+// One block per SM (more or less): each writes its SM's cycle counter and the global timer.
+__global__ void sample_sm_clocks_kernel(long long* out, int max_sms) {
+  if (threadIdx.x != 0) return;
+  uint32_t smid;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+  if (int(smid) >= max_sms) return;
+  unsigned long long timer;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(timer));
+  out[2 * smid] = clock64();
+  out[2 * smid + 1] = static_cast<long long>(timer);
+}
+
 #if defined(B200ATTN_TRACE) || defined(B200ATTN_PROFILE)
 // Timeline studies only (never compiled into the shipped library): where block 0 records clock64.
 static long long* g_trace_buffer = nullptr;
@@ -376,6 +388,20 @@ int b200attn_set_wait_limit_ms(uint32_t ms) {
 }
 
 uint64_t b200attn_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int b200attn_sample_sm_clocks(int64_t* out, int32_t max_sms, void* stream) {
+  if (out == nullptr || max_sms < 1) return fail(B200ATTN_ERR_INVALID_ARGUMENT, "null buffer or max_sms < 1");
+  int device = 0;
+  DeviceState* st = nullptr;
+  const int rc = get_device(&device, &st);
+  if (rc != 0) return rc;
+  // twice as many blocks as SMs, one warp each: every SM that is not completely full gets one
+  sample_sm_clocks_kernel<<<2 * st->sm_count, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<long long*>(out), max_sms);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail_cuda("clock sample launch", e);
+  return B200ATTN_OK;
+}
 
 int b200attn_ipc_export(const void* device_ptr, unsigned char handle[64], uint64_t* offset_bytes) {
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");

@@ -64,19 +64,6 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
-// True in exactly one (hardware-chosen) lane of a converged warp.
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p_e;\n\t"
-      "elect.sync _|p_e, 0xffffffff;\n\t"
-      "selp.u32 %0, 1, 0, p_e;\n\t"
-      "}\n"
-      : "=r"(pred));
-  return pred != 0;
-}
-
 // ----------------------------------------------------------------------------- proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -321,10 +308,6 @@ __device__ __forceinline__ void f2_split(f2 v, float& lo, float& hi) {
   asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v.bits));
 }
 
-__device__ __forceinline__ void f2_split_u32(f2 v, uint32_t& lo, uint32_t& hi) {
-  asm("mov.b64 {%0, %1}, %2;\n" : "=r"(lo), "=r"(hi) : "l"(v.bits));
-}
-
 __device__ __forceinline__ f2 f2_fma(f2 a, f2 b, f2 c) {
   f2 r;
   asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(r.bits) : "l"(a.bits), "l"(b.bits), "l"(c.bits));
@@ -337,61 +320,10 @@ __device__ __forceinline__ f2 f2_add(f2 a, f2 b) {
   return r;
 }
 
-// Round-toward-minus-infinity add: used to extract floor(x) with a magic constant.
-__device__ __forceinline__ f2 f2_add_rm(f2 a, f2 b) {
-  f2 r;
-  asm("add.rm.f32x2 %0, %1, %2;\n" : "=l"(r.bits) : "l"(a.bits), "l"(b.bits));
-  return r;
-}
-
-__device__ __forceinline__ f2 f2_sub(f2 a, f2 b) {
-  f2 r;
-  asm("sub.rn.f32x2 %0, %1, %2;\n" : "=l"(r.bits) : "l"(a.bits), "l"(b.bits));
-  return r;
-}
-
 // Two bf16 in one 32-bit word: `lo` in bits 0..15, `hi` in bits 16..31.
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;\n" : "=r"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-
-// Round-toward-minus-infinity fused multiply-add on a pair.
-__device__ __forceinline__ f2 f2_fma_rm(f2 a, f2 b, f2 c) {
-  f2 r;
-  asm("fma.rm.f32x2 %0, %1, %2, %3;\n" : "=l"(r.bits) : "l"(a.bits), "l"(b.bits), "l"(c.bits));
-  return r;
-}
-
-// 2^(s * c - m) for a pair of scores without touching the MUFU unit, for an INTEGER-valued m
-// with |m| < 2^21 and scores clamped by the caller so that s * c - m >= -126.
-//   magic_minus_m = 1.5 * 2^23 - m is exactly representable (that is what the integer m buys), so
-//   t = RD(s * c + magic_minus_m) = 1.5 * 2^23 + floor(s * c - m) in one instruction: the low
-//   mantissa bits of t hold n = floor(x). magic_minus_m - t = -(n + m) is exact, so
-//   f = s * c - (n + m) = x - n in [0, 1) is one more fused multiply-add on the raw score.
-//   2^f is a cubic (max relative error 8.6e-5; weighted minimax fit with p(0) = 1) and 2^n is
-//   applied by adding n << 23 to the exponent field (the bits of t above its low nine vanish in
-//   the shift).
-// Six FMA-pipe cycles and one integer instruction per element, against eight MUFU cycles.
-__device__ __forceinline__ f2 exp2_poly_scaled(f2 s, f2 c, f2 magic_minus_m) {
-  const f2 t = f2_fma_rm(s, c, magic_minus_m);
-  const f2 g = f2_sub(magic_minus_m, t);
-  const f2 fr = f2_fma(s, c, g);
-#if defined(B200ATTN_POLY_DEG2)
-  f2 p = f2_fma(f2_splat(0.32991594f), fr, f2_splat(0.66597021f));
-#else
-  f2 p = f2_fma(f2_splat(0.07706520f), fr, f2_splat(0.22764701f));
-  p = f2_fma(p, fr, f2_splat(0.69511634f));
-#endif
-  p = f2_fma(p, fr, f2_splat(1.0f));
-  uint32_t p0, p1, t0, t1;
-  f2_split_u32(p, p0, p1);
-  f2_split_u32(t, t0, t1);
-  p0 += t0 << 23;
-  p1 += t1 << 23;
-  f2 r;
-  asm("mov.b64 %0, {%1, %2};\n" : "=l"(r.bits) : "r"(p0), "r"(p1));
   return r;
 }
 

@@ -90,6 +90,7 @@ class RingAttention:
         self._copy_stream = None
         self._events = None
         self._ready = None
+        self._timing = None
 
     def _meet(self) -> None:
         import torch.distributed as dist
@@ -183,8 +184,21 @@ class RingAttention:
         self._native.device_check()
 
     # -- the ring ----------------------------------------------------------------------------
+    def last_timing(self):
+        """Of the last `forward(..., timing=True)` call, after `synchronize()`: per-step peer pull
+        and kernel durations (ms) and the time the compute stream sat waiting for a pull."""
+        if self._timing is None:
+            return None
+        pulls, kernels = self._timing
+        pull_ms = [a.elapsed_time(b) for a, b in pulls[1:]]
+        kernel_ms = [a.elapsed_time(b) for a, b in kernels]
+        exposed = 0.0
+        for s in range(1, len(kernels)):
+            exposed += max(0.0, kernels[s - 1][1].elapsed_time(pulls[s][1]))
+        return {"pull_ms": pull_ms, "kernel_ms": kernel_ms, "exposed_ms": exposed}
+
     def forward(self, q, k_local, v_local, *, softmax_scale: float = 0.0, return_lse: bool = True,
-                out=None):
+                out=None, timing: bool = False):
         import torch
 
         from . import ops
@@ -212,6 +226,8 @@ class RingAttention:
             self._ready = torch.cuda.Event()
         copied, consumed = self._events
         result = None
+        tev = lambda: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        self._timing = ([tev() for _ in range(self.world)], [tev() for _ in range(self.world)]) if timing else None
 
         # Entry: whatever wrote this rank's K/V (on the current stream) has finished, on every
         # rank, before anybody pulls. The ranks also agree here on whether the shards have to be
@@ -228,8 +244,12 @@ class RingAttention:
             with torch.cuda.stream(side):
                 if step >= 2:
                     side.wait_event(consumed[step - 2])  # the buffer's previous occupant was read
+                if timing:
+                    self._timing[0][step][0].record(side)
                 N.check(lib.b200attn_copy_async(buf[0].data_ptr(), peer.k_ptr, nbytes, side.cuda_stream))
                 N.check(lib.b200attn_copy_async(buf[1].data_ptr(), peer.v_ptr, nbytes, side.cuda_stream))
+                if timing:
+                    self._timing[0][step][1].record(side)
                 copied[step].record(side)
 
         if self.world > 1:
@@ -241,9 +261,13 @@ class RingAttention:
                 main.wait_event(copied[step])
                 k_cur, v_cur = self._staging[step % 2]
             merge, emit = flags[step]
+            if timing:
+                self._timing[1][step][0].record(main)
             result = ops.attention(q, k_cur, v_cur, softmax_scale=softmax_scale, return_lse=True,
                                    out=out, partial=self._partial if self.world > 1 else None,
                                    partial_merge=merge, partial_emit=emit)
+            if timing:
+                self._timing[1][step][1].record(main)
             consumed[step].record(main)
             if step + 2 < self.world:
                 start_pull(step + 2)

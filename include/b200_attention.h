@@ -122,6 +122,15 @@ B200ATTN_API int b200attn_device_check(int device, int32_t record[8]);
 /* Limit for device-side waits, milliseconds (default 2000). Applies to later launches. */
 B200ATTN_API int b200attn_set_wait_limit_ms(uint32_t ms);
 
+/* Measurement aid (no counterpart in the reference project): records, for every SM a block of this
+ * tiny kernel lands on, the SM's cycle counter and the global nanosecond timer, on `stream`.
+ * `out` is device memory for 2 * max_sms int64 values: out[2 * smid] = clock64, out[2 * smid + 1]
+ * = globaltimer (SMs with smid >= max_sms are skipped; entries of SMs no block ran on keep their
+ * old contents, so clear the buffer first). Two samples around a timed region give the average
+ * SM clock over exactly that region: (clock64_after - clock64_before) / (timer_after -
+ * timer_before) per SM. Does not count towards b200attn_launch_count. */
+B200ATTN_API int b200attn_sample_sm_clocks(int64_t* out, int32_t max_sms, void* stream);
+
 /* Number of kernels this library has launched in this process (all devices, all streams). */
 B200ATTN_API uint64_t b200attn_launch_count(void);
 
