@@ -32,6 +32,7 @@ NOALLOC_MAX_ROWS = 16384
 # Every symbol include/b200_attention.h declares (the CPU tests check the library exports all).
 EXPORTED_SYMBOLS = (
     "b200attn_forward",
+    "b200attn_workspace_bytes",
     "b200attn_bhld_launch",
     "b200attn_bshd_launch",
     "b200attn_forward_kv_split_noalloc",
@@ -86,6 +87,8 @@ class ForwardArgs(C.Structure):
         ("stream", C.c_void_p),
         ("causal", C.c_int32),
         ("heads_kv", C.c_int32),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_uint64),
     ]
 
 
@@ -103,6 +106,8 @@ def lib() -> C.CDLL:
         handle = C.CDLL(str(CORE_LIB), mode=C.RTLD_GLOBAL)
         handle.b200attn_forward.argtypes = [C.POINTER(ForwardArgs)]
         handle.b200attn_forward.restype = C.c_int
+        handle.b200attn_workspace_bytes.argtypes = [C.POINTER(C.c_uint64)]
+        handle.b200attn_workspace_bytes.restype = C.c_int
         launch8 = [C.c_void_p] * 4 + [C.c_int] * 3 + [C.c_void_p]
         handle.b200attn_bhld_launch.argtypes = launch8
         handle.b200attn_bhld_launch.restype = C.c_int
@@ -147,7 +152,13 @@ def check(status: int) -> None:
 def device_check(device: int = -1) -> None:
     """Raise if a kernel launched on `device` left early. Synchronise the stream first."""
     rec = (C.c_int32 * 8)()
-    check(lib().b200attn_device_check(device, rec))
+    status = lib().b200attn_device_check(device, rec)
+    if status != STATUS_OK:
+        # a kernel that left early may have left split counters behind: start from fresh workspaces
+        from . import ops
+
+        ops.drop_workspaces()
+    check(status)
 
 
 def launch_count() -> int:

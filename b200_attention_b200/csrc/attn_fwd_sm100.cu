@@ -409,6 +409,87 @@ __device__ __forceinline__ int item_tiles(const FwdParams& p, int row0) {
   return q_tile_tiles<kCausal>(p, row0, kQTilesPerItem - 1);
 }
 
+// ---- work distribution ----------------------------------------------------------------------
+// A piece is K/V tiles [t0, t1) of one work item. Without splitting (kSplit == false) a piece is a
+// whole item and CTA c takes items c, c + grid, c + 2 * grid, ... With splitting, the full rounds
+// are dealt the same way (all CTAs then stream the K/V of the same few heads at the same time,
+// which is what keeps K/V in L2), and only the items of the last, partly filled round are treated
+// differently (and taken first, see PieceWalk::take): the sequence of their (item, tile) pairs, item-major, is cut into one contiguous
+// run per CTA of near-equal length, so every CTA gets the same amount of tensor work whatever
+// items % grid is. A CTA's run is a (possibly cut) first item, whole items, and a (possibly cut)
+// last item. A run boundary that would leave a piece shorter than kSplitMinPieceTiles snaps to the
+// item boundary. Every role of a CTA walks the same pieces in the same order.
+// (Units are counted in 32 bits: the host only splits launches with fewer than 2^31 of them.)
+__device__ __forceinline__ int split_first_item(const FwdParams& p, int grid) {
+  return (p.total_items / grid) * grid;  // items before this one belong to full rounds
+}
+// How many CTAs (the first ones) share the last round's items is the host's choice: every run is
+// at least kSplitMinPieceTiles long, so a run that lies strictly inside an item is never empty.
+__device__ __forceinline__ int split_runs(const FwdParams& p, int /*grid*/) { return p.split_runs; }
+// First unit of CTA c's run; units number the (item, tile) pairs of the last round's items.
+__device__ __forceinline__ int split_cut(const FwdParams& p, int c, int grid) {
+  const long long total = static_cast<long long>(p.total_items - split_first_item(p, grid)) * p.kv_tiles;
+  const int runs = split_runs(p, grid);
+  if (c >= runs) return int(total);
+  int u = int(total * c / runs);
+  const int r = u % p.kv_tiles;
+  if (r < kSplitMinPieceTiles) u -= r;
+  else if (p.kv_tiles - r < kSplitMinPieceTiles) u += p.kv_tiles - r;
+  return u;
+}
+// The CTA whose run holds unit u.
+__device__ __forceinline__ int split_owner(const FwdParams& p, int u, int grid) {
+  const long long total = static_cast<long long>(p.total_items - split_first_item(p, grid)) * p.kv_tiles;
+  const int runs = split_runs(p, grid);
+  int c = int(static_cast<long long>(u) * runs / total);
+  while (c + 1 < runs && split_cut(p, c + 1, grid) <= u) ++c;
+  while (c > 0 && split_cut(p, c, grid) > u) --c;
+  return c;
+}
+
+struct Piece {
+  int item, t0, t1;  // K/V tiles [t0, t1) of work item `item`
+};
+
+// Hands out a CTA's pieces one by one. Between two pieces only (item, u, u_end) are live.
+template <bool kSplit>
+struct PieceWalk {
+  int item;      // the next whole item of the full rounds
+  int u, u_end;  // kSplit: first unit of the next piece of the last round, end of this CTA's run
+
+  __device__ __forceinline__ explicit PieceWalk(const FwdParams& p) {
+    item = int(blockIdx.x);
+    if (kSplit) {
+      u = split_cut(p, int(blockIdx.x), int(gridDim.x));
+      u_end = split_cut(p, int(blockIdx.x) + 1, int(gridDim.x));
+    } else {
+      u = u_end = 0;
+    }
+  }
+  // The next piece, if there is one. The run through the last round's items comes first and the
+  // whole items of the full rounds after it: the merge of a cut item (done by the epilogue warps
+  // of whichever CTA finishes its piece last) then overlaps that CTA's remaining whole items
+  // instead of standing at the end of the launch.
+  __device__ __forceinline__ bool take(const FwdParams& p, Piece& out) {
+    const int whole_items = kSplit ? split_first_item(p, int(gridDim.x)) : p.total_items;
+    if (kSplit && u < u_end) {
+      const int k = u / p.kv_tiles;
+      out.item = whole_items + k;
+      out.t0 = u - k * p.kv_tiles;
+      const int left = u_end - u;
+      out.t1 = (left < p.kv_tiles - out.t0) ? out.t0 + left : p.kv_tiles;
+      u += out.t1 - out.t0;
+      return true;
+    }
+    if (item >= whole_items) return false;
+    out.item = item;
+    out.t0 = 0;
+    out.t1 = p.kv_tiles;
+    item += int(gridDim.x);
+    return true;
+  }
+};
+
 // ---- TMA producer -------------------------------------------------------------------------
 __device__ __forceinline__ void load_tile(uint32_t lead, uint32_t dst, const CUtensorMap* map,
                                           int row, int h, int b, uint32_t bar) {
@@ -417,7 +498,7 @@ __device__ __forceinline__ void load_tile(uint32_t lead, uint32_t dst, const CUt
   tma_load_4d_lead(lead, dst + kBoxBytes, map, 64, row, h, b, bar);
 }
 
-template <bool kCausal>
+template <bool kCausal, bool kSplit>
 __device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CUtensorMap* tk,
                              const CUtensorMap* tv, uint32_t smem_q, uint32_t smem_kv,
                              uint32_t bar0, uint32_t lead, WaitCtx& w) {
@@ -459,16 +540,21 @@ __device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CU
   };
 
   bool first = true;
-  for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
+  PieceWalk<kSplit> pw(p);
+  Piece pc;
+  while (ok && pw.take(p, pc)) {
+    const int item = pc.item;
     const ItemCoord c = decode_item<kCausal>(p, item);
-    const int T = item_tiles<kCausal>(p, c.row0);
+    // tiles [tb, tb + T) of the item's K/V stream
+    const int tb = kSplit ? pc.t0 : 0;
+    const int T = kSplit ? pc.t1 - pc.t0 : item_tiles<kCausal>(p, c.row0);
     // K/V coordinates: grouped-query attention maps kv_group query heads onto one K/V head
     ItemCoord kvc = c;
     kvc.h = c.h / p.kv_group;
     w.item = item;
     w.tile = 0;
     if (first) {
-      ok = push_pair(false, 0, kvc, true, 0, kvc, 110);  // K_0 of the first item travels alone
+      ok = push_pair(false, 0, kvc, true, tb * kBlockN, kvc, 110);  // the first K tile travels alone
       first = false;
       if (!ok) break;
     }
@@ -485,17 +571,19 @@ __device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CU
     for (int i = 0; ok && i < T; ++i) {
       w.tile = i;
       if (i + 1 < T) {
-        ok = push_pair(true, i * kBlockN, kvc, true, (i + 1) * kBlockN, kvc, 111);
+        ok = push_pair(true, (tb + i) * kBlockN, kvc, true, (tb + i + 1) * kBlockN, kvc, 111);
       } else {
-        // the last V of this item shares its pair with K_0 of the CTA's next item, if any
-        const int next_item = item + int(gridDim.x);
-        const bool has_next_item = next_item < p.total_items;
+        // the last V of this piece shares its pair with the first K of the CTA's next piece, if any
+        PieceWalk<kSplit> ahead = pw;
+        Piece np;
+        const bool has_next_piece = ahead.take(p, np);
         ItemCoord next_kvc = kvc;
-        if (has_next_item) {
-          next_kvc = decode_item<kCausal>(p, next_item);
+        if (has_next_piece) {
+          next_kvc = decode_item<kCausal>(p, np.item);
           next_kvc.h /= p.kv_group;
         }
-        ok = push_pair(true, i * kBlockN, kvc, has_next_item, 0, next_kvc, 112);
+        ok = push_pair(true, (tb + i) * kBlockN, kvc, has_next_piece,
+                       (kSplit && has_next_piece ? np.t0 : 0) * kBlockN, next_kvc, 112);
       }
     }
   }
@@ -608,7 +696,7 @@ __device__ void ws_mma_role_causal(const FwdParams& p, uint32_t smem_q, uint32_t
   }
 }
 
-template <bool kCausal>
+template <bool kCausal, bool kSplit>
 __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_kv, uint32_t bar0,
                             uint32_t tmem_base, uint32_t lead, WaitCtx& w) {
   if (kCausal) {
@@ -629,11 +717,14 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
 
   PROF_DECL(8);  // 0 other, 1 wait pair, 3 wait P (+O_FREE), 4 issue PV, 5 issue QK, 6 commits
 
-  for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
-    const int T = p.kv_tiles;
+  PieceWalk<kSplit> pw(p);
+  Piece pc;
+  while (ok && pw.take(p, pc)) {
+    const int item = pc.item;
+    const int T = pc.t1 - pc.t0;
     w.item = item;
     w.tile = 0;
-    // ---- tile 0 scores for both Q tiles
+    // ---- first scores of the piece for both Q tiles
     if (!k_ready) {
       if (!(ok = w.wait_issue(bar(kBarPairFull + slot), full_parity, 200))) break;
       slot ^= 1u;
@@ -754,7 +845,7 @@ __device__ __forceinline__ float f2_hsum(f2 a, f2 b) {
 // retract. All exponentials run on the MUFU unit and P is handed over in one piece: handing the
 // first columns over early, an FMA-pipe polynomial for part of the exponentials, and storing P
 // chunk by chunk as it is produced each measured slower in this kernel.
-template <bool kCausal>
+template <bool kCausal, bool kSplit>
 __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, uint32_t tmem_base,
                                 int q, int warp_in_group, int lane, WaitCtx& w) {
   auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
@@ -778,7 +869,10 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
   uint32_t fin_free_parity = 1;  // passes on the fresh barrier: nothing to consume yet
   PROF_DECL(8);  // 0 other, 1 wait S, 2 TMEM load, 3 exponentials + check, 4 store + signal
 
-  for (int item = blockIdx.x; item < p.total_items; item += gridDim.x) {
+  PieceWalk<kSplit> pw(p);
+  Piece pc;
+  while (pw.take(p, pc)) {
+    const int item = pc.item;
     w.item = item;
     w.tile = 0;
     // The epilogue warps must have consumed the previous item's final (max, sum) before this
@@ -792,7 +886,10 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
     float l = 0.0f;     // running sum of 2^(s - m)
     // causal: this row sees keys 0 .. row + causal_off; its Q tile's first row sees the fewest
     const int row0 = kCausal ? decode_item<true>(p, item).row0 : 0;
-    const int T = q_tile_tiles<kCausal>(p, row0, q);
+    // this piece's tiles are tiles [tb, tb + T) of the item (a piece starts its own partial result)
+    const int tb = kSplit ? pc.t0 : 0;
+    const int T = kSplit ? pc.t1 - pc.t0 : q_tile_tiles<kCausal>(p, row0, q);
+    const int ragged_i = last_tile - tb;  // the piece's tile that holds the ragged end of the keys, if any
     const int tile_limit = row0 + q * kBlockM + p.causal_off;  // last key the tile's first row sees
     const int row_limit = tile_limit + r;                      // last key this row sees
     for (int i = 0; i < T; ++i) {
@@ -815,7 +912,7 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
       if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 2);
       // keys of this tile that exist for this row: all 128, fewer in a ragged last tile, and with
       // a causal mask fewer (possibly none) in the tiles the diagonal crosses
-      bool tail = (i == last_tile && tail_valid < kBlockN);
+      bool tail = (i == ragged_i && tail_valid < kBlockN);
       int valid = tail ? tail_valid : kBlockN;
       if (kCausal && i * kBlockN + kBlockN - 1 > tile_limit) {
         tail = true;
@@ -887,7 +984,14 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
+#ifdef B200ATTN_TEST_DROP_P_READY
+      // Test builds only (never the shipped library): one warp withholds one arrival, so that the
+      // bounded waits of every role run out and the CTA leaves with a recorded timeout.
+      const bool withheld = (q == 0 && warp_in_group == 0 && item == 0 && i == 1);
+      mbar_arrive_lead((lane == 0 && !withheld) ? 1u : 0u, bar(kBarPReady + q));
+#else
       mbar_arrive_lead(lane == 0 ? 1u : 0u, bar(kBarPReady + q));
+#endif
       PROF_LAP(4);
       if (tr) B200ATTN_TRACE_EVENT(p, q, item, i, 0, 4);
       l += tile_sum;
@@ -903,9 +1007,109 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
 }
 
 // ---- epilogue -------------------------------------------------------------------------------
-// Once per item and Q tile: take the final (max, sum) from the softmax group, read the
+// A cut piece's partial result and, for the piece that finishes last, the merge of the item.
+// Called by one epilogue warp for its 32 rows of Q tile q, after the piece's partial (normalised
+// fp32 O and LSE) has been stored to this CTA's slot. Nobody waits for another CTA: every piece
+// stores, fences and takes a ticket; whoever draws the last ticket finds every partial in memory
+// and writes the item's bf16 O and LSE.
+//
+// The pieces of an item belong to consecutive CTAs c_first .. c_last (runs strictly inside an item
+// are never empty), in slot 0 of each except possibly c_first, whose run may have begun before
+// the item. The merge first finds every row's total LSE (one row per lane), then walks the rows
+// with the whole warp on one row at a time, so that partial rows are read and the output row is
+// written as whole 512- and 256-byte lines.
+__device__ void split_merge_rows(const FwdParams& p, const Piece& pc, const ItemCoord& c, int q,
+                                 int warp_in_group, int lane) {
+  const int grid = int(gridDim.x);
+  const int T = p.kv_tiles;
+  const int item_u0 = (pc.item - split_first_item(p, grid)) * T;
+  const int c_first = split_owner(p, item_u0, grid);
+  const int c_last = split_owner(p, item_u0 + T - 1, grid);
+  const int pieces = c_last - c_first + 1;
+
+  // every lane's stores are ordered before the ticket
+  __threadfence();
+  __syncwarp();
+  int32_t* ticket = p.split_tickets + c_first * kSplitTicketsPerCta + q * 4 + warp_in_group;
+  int drawn = 0;
+  if (lane == 0) drawn = atomicAdd(ticket, 1);
+  drawn = __shfl_sync(0xffffffffu, drawn, 0);
+  if (drawn != pieces - 1) return;
+  if (lane == 0) *ticket = 0;  // ready for the next launch
+  __threadfence();
+
+  const int first_which = split_cut(p, c_first, grid) < item_u0 ? 1 : 0;
+  const float* slot0 = p.split_scratch + (size_t(c_first) * 2 + first_which) * kSplitSlotFloats;
+  auto slot_of = [&](int k) -> const float* {  // k-th piece of the item
+    return k == 0 ? slot0 : p.split_scratch + size_t(c_first + k) * 2 * kSplitSlotFloats;
+  };
+  const int rs0 = q * kBlockM + warp_in_group * 32;  // first of this warp's rows inside a slot
+  // pass 1 (one row per lane): the row's total LSE and the weights of its first four pieces
+  float top = kNegInf, sum = 0.0f;
+  float lse_k[4] = {kNegInf, kNegInf, kNegInf, kNegInf};
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    if (k < pieces) lse_k[k] = __ldcg(slot_of(k) + kItemRows * kHeadDim + rs0 + lane);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) top = fmaxf(top, lse_k[k]);
+  for (int k = 4; k < pieces; ++k) top = fmaxf(top, __ldcg(slot_of(k) + kItemRows * kHeadDim + rs0 + lane));
+#pragma unroll
+  for (int k = 0; k < 4; ++k) sum += expf(lse_k[k] - top);  // exp(-inf) = 0 for absent pieces
+  for (int k = 4; k < pieces; ++k) sum += expf(__ldcg(slot_of(k) + kItemRows * kHeadDim + rs0 + lane) - top);
+  const float lse_mine = top + logf(sum);
+  float w_k[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) w_k[k] = expf(lse_k[k] - lse_mine);
+  const int row_mine = c.row0 + rs0 + lane;
+  if (row_mine < p.len_q && p.lse != nullptr)
+    p.lse[(int64_t(c.b) * p.heads + c.h) * p.len_q + row_mine] = lse_mine;
+
+  // pass 2: four rows per step, the whole warp on each row (lane l holds columns 4l .. 4l+3), every
+  // load of a step in flight before the first use
+  __nv_bfloat16* o_base = p.o + int64_t(c.b) * p.o_stride_b + int64_t(c.h) * p.o_stride_h;
+#pragma unroll 1
+  for (int rr = 0; rr < 32; rr += 4) {
+    float4 acc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < pieces; ++k) {
+      const float* slot = slot_of(k);
+      float4 a[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        a[j] = __ldcg(reinterpret_cast<const float4*>(slot + size_t(rs0 + rr + j) * kHeadDim) + lane);
+      float wgt[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float w0 = __shfl_sync(0xffffffffu, w_k[0], rr + j), w1 = __shfl_sync(0xffffffffu, w_k[1], rr + j);
+        const float w2 = __shfl_sync(0xffffffffu, w_k[2], rr + j), w3 = __shfl_sync(0xffffffffu, w_k[3], rr + j);
+        const float lt = __shfl_sync(0xffffffffu, lse_mine, rr + j);
+        wgt[j] = k == 0 ? w0 : k == 1 ? w1 : k == 2 ? w2 : k == 3 ? w3
+                 : expf(__ldcg(slot + kItemRows * kHeadDim + rs0 + rr + j) - lt);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[j].x = fmaf(a[j].x, wgt[j], acc[j].x);
+        acc[j].y = fmaf(a[j].y, wgt[j], acc[j].y);
+        acc[j].z = fmaf(a[j].z, wgt[j], acc[j].z);
+        acc[j].w = fmaf(a[j].w, wgt[j], acc[j].w);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int row = c.row0 + rs0 + rr + j;
+      if (row >= p.len_q) continue;  // uniform across the warp
+      uint2 out;
+      out.x = pack_bf16x2(acc[j].x, acc[j].y);
+      out.y = pack_bf16x2(acc[j].z, acc[j].w);
+      *reinterpret_cast<uint2*>(o_base + int64_t(row) * p.o_stride_l + lane * 4) = out;
+    }
+  }
+}
+
+// Once per piece and Q tile: take the final (max, sum) from the softmax group, read the
 // accumulator out of TMEM, normalise, optionally merge with a stored partial, store O / LSE.
-template <bool kCausal>
+template <bool kCausal, bool kSplit>
 __device__ void ws_epilogue_role(const FwdParams& p, WsAux* aux, uint32_t bar0, uint32_t tmem_base,
                                  int warp_in_group, int lane, WaitCtx& w) {
   auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
@@ -913,10 +1117,14 @@ __device__ void ws_epilogue_role(const FwdParams& p, WsAux* aux, uint32_t bar0, 
   const int r = warp_in_group * 32 + lane;
   uint32_t fin_parity = 0;
 
-  for (int item = blockIdx.x; item < p.total_items; item += gridDim.x) {
+  PieceWalk<kSplit> pw(p);
+  Piece pc;
+  while (pw.take(p, pc)) {
+    const int item = pc.item;
     w.item = item;
     w.tile = p.kv_tiles;
     const ItemCoord c = decode_item<kCausal>(p, item);
+    const bool cut = kSplit && (pc.t0 > 0 || pc.t1 < p.kv_tiles);
     for (int q = 0; q < kQTilesPerItem; ++q) {
       if (!w.wait_warp(bar(kBarFin + q), fin_parity, 410 + q)) return;
       if (!w.wait_warp(bar(kBarPvDone + q), fin_parity, 420 + q)) return;
@@ -925,20 +1133,48 @@ __device__ void ws_epilogue_role(const FwdParams& p, WsAux* aux, uint32_t bar0, 
       const float fin_l = aux->row_sum[q][r];
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kBarFinFree + q));
-      const RowOut out = make_row_out(p, c.b, c.h, c.row0 + q * kBlockM + r, fin_m, fin_l);
+      const int row = c.row0 + q * kBlockM + r;
+      RowOut out;
+      if (cut) {
+        // this piece covers only part of the item's keys: leave a partial in this CTA's slot
+        // (slot 0 if the piece opens the CTA's run, else slot 1)
+        const int unit = (item - split_first_item(p, int(gridDim.x))) * p.kv_tiles + pc.t0;
+        const bool opens_run = unit == split_cut(p, int(blockIdx.x), int(gridDim.x));
+        float* slot = p.split_scratch + (size_t(blockIdx.x) * 2 + (opens_run ? 0 : 1)) * kSplitSlotFloats;
+        const int rs = q * kBlockM + r;
+        out.valid = row < p.len_q;
+        out.o_row = nullptr;
+        out.part_row = slot + size_t(rs) * kHeadDim;
+        out.w_cur = 1.0f / fin_l;
+        out.w_prev = 0.0f;
+        out.emit_partial = true;
+        if (out.valid) slot[kItemRows * kHeadDim + rs] = (fin_m + log2f(fin_l)) * kLn2;
+      } else {
+        out = make_row_out(p, c.b, c.h, row, fin_m, fin_l);
+      }
       const uint32_t o_tmem = tmem_base + kQTilesPerItem * kBlockN + q * kHeadDim + lane_field;
       store_row(out, o_tmem, [&]() {
-        // O_q is in registers: the next item's first PV may overwrite it.
+        // O_q is in registers: the next piece's first PV may overwrite it.
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(kBarOFree + q));
       });
     }
+    // Both accumulators have been handed back: the tickets and (for the piece that finishes last)
+    // the merge now run beside the CTA's next piece.
+    if constexpr (kSplit) {
+      if (cut) {
+        for (int q = 0; q < kQTilesPerItem; ++q) {
+          split_merge_rows(p, pc, c, q, warp_in_group, lane);
+          __syncwarp();
+        }
+      }
+    }
     fin_parity ^= 1u;
   }
 }
 
-template <bool kCausal>
+template <bool kCausal, bool kSplit>
 __global__ void __launch_bounds__(kWsThreads, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
                    const __grid_constant__ CUtensorMap tmap_k,
@@ -998,15 +1234,15 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
   if (warp < 8) {
     reg_grow<kRegsSoftmax>();
-    ws_softmax_role<kCausal>(p, aux, bar0, tmem_base, warp >> 2, warp & 3, lane, w);
+    ws_softmax_role<kCausal, kSplit>(p, aux, bar0, tmem_base, warp >> 2, warp & 3, lane, w);
   } else if (warp < 12) {
     reg_shrink<kRegsEpilogue>();
-    ws_epilogue_role<kCausal>(p, aux, bar0, tmem_base, warp & 3, lane, w);
+    ws_epilogue_role<kCausal, kSplit>(p, aux, bar0, tmem_base, warp & 3, lane, w);
   } else {
     reg_shrink<kRegsOther>();
     const uint32_t lead = (lane == 0) ? 1u : 0u;
     if (warp == 12) {
-      ws_mma_role<kCausal>(p, smem_q, smem_kv, bar0, tmem_base, lead, w);
+      ws_mma_role<kCausal, kSplit>(p, smem_q, smem_kv, bar0, tmem_base, lead, w);
     } else if (warp == 13) {
       if (lead) {
         tma_prefetch_desc(&tmap_q);
@@ -1014,7 +1250,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
         tma_prefetch_desc(&tmap_v);
       }
       __syncwarp();
-        ws_load_role<kCausal>(p, &tmap_q, &tmap_k, &tmap_v, smem_q, smem_kv, bar0, lead, w);
+        ws_load_role<kCausal, kSplit>(p, &tmap_q, &tmap_k, &tmap_v, smem_q, smem_kv, bar0, lead, w);
     }
     __syncwarp();
   }
@@ -1210,8 +1446,9 @@ cudaError_t prepare_kernels() {
   // blocks in hardware until the CTA's pool has room, so refuse to run unless the pool the
   // launch reserves (registers per thread x 512 threads) covers what the roles ask for.
   constexpr int kPoolNeeded = 128 * (2 * kRegsSoftmax + kRegsEpilogue + kRegsOther);
-  const void* ws_kernels[2] = {reinterpret_cast<const void*>(&attn_fwd_ws_kernel<false>),
-                               reinterpret_cast<const void*>(&attn_fwd_ws_kernel<true>)};
+  const void* ws_kernels[3] = {reinterpret_cast<const void*>(&attn_fwd_ws_kernel<false, false>),
+                               reinterpret_cast<const void*>(&attn_fwd_ws_kernel<true, false>),
+                               reinterpret_cast<const void*>(&attn_fwd_ws_kernel<false, true>)};
   for (const void* kernel : ws_kernels) {
     cudaFuncAttributes fa;
     cudaError_t e = cudaFuncGetAttributes(&fa, kernel);
@@ -1224,13 +1461,44 @@ cudaError_t prepare_kernels() {
                               kSerialSmemBytes);
 }
 
+SplitPlan split_plan(const FwdParams& p, int sm_count) {
+  const SplitPlan none{0, 0};
+  if (p.causal || p.partial.merge || p.partial.emit || p.kv_tiles < 2 * kSplitMinPieceTiles) return none;
+  if (static_cast<long long>(p.total_items) * p.kv_tiles >= (1ll << 31)) return none;
+  // the last, partly filled round of whole items is what gets cut into equal runs
+  const int tail_items = p.total_items % sm_count;
+  if (tail_items == 0) return none;
+  const bool full_rounds = p.total_items >= sm_count;
+  const long long tail_units = static_cast<long long>(tail_items) * p.kv_tiles;
+  long long runs = tail_units / kSplitMinPieceTiles;
+  if (runs > sm_count) runs = sm_count;
+  // Without full rounds behind it the merge of a cut item stands at the end of the launch, and it
+  // costs about six tile periods per piece: keep the pieces per item few.
+  constexpr int kExposedPiecesPerItem = 4, kMergeTilesPerPiece = 6;
+  if (!full_rounds && runs > static_cast<long long>(tail_items) * kExposedPiecesPerItem)
+    runs = static_cast<long long>(tail_items) * kExposedPiecesPerItem;
+  if (runs < 1) return none;
+  const int grid = full_rounds ? sm_count : int(runs);
+  // tiles on the busiest CTA: whole items dealt round-robin, against full rounds plus one even run
+  // per CTA (which pays for up to two cut pieces: their extra Q loads and partial stores, about
+  // three tile periods, and for an exposed merge)
+  const int rounds_grid = full_rounds ? sm_count : p.total_items;
+  const long long legacy = static_cast<long long>((p.total_items + rounds_grid - 1) / rounds_grid) * p.kv_tiles;
+  const long long pieces_per_item = (runs + tail_items - 1) / tail_items + 1;
+  const long long split = static_cast<long long>(p.total_items / sm_count) * p.kv_tiles + (tail_units + runs - 1) / runs +
+                          3 + (full_rounds ? 0 : kMergeTilesPerPiece * pieces_per_item);
+  return (split * 100 < legacy * 97) ? SplitPlan{grid, int(runs)} : none;
+}
+
 cudaError_t launch_fwd_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                           const FwdParams& p, int sm_count, cudaStream_t stream) {
   const int grid = p.total_items < sm_count ? p.total_items : sm_count;
   if (p.causal) {
-    attn_fwd_ws_kernel<true><<<grid, kWsThreads, kWsSmemBytes, stream>>>(tq, tk, tv, p);
+    attn_fwd_ws_kernel<true, false><<<grid, kWsThreads, kWsSmemBytes, stream>>>(tq, tk, tv, p);
+  } else if (p.split_scratch != nullptr) {
+    attn_fwd_ws_kernel<false, true><<<split_plan(p, sm_count).grid, kWsThreads, kWsSmemBytes, stream>>>(tq, tk, tv, p);
   } else {
-    attn_fwd_ws_kernel<false><<<grid, kWsThreads, kWsSmemBytes, stream>>>(tq, tk, tv, p);
+    attn_fwd_ws_kernel<false, false><<<grid, kWsThreads, kWsSmemBytes, stream>>>(tq, tk, tv, p);
   }
   return cudaGetLastError();
 }

@@ -52,12 +52,35 @@ struct FwdParams {
   int32_t* status;      // kStatusInts ints the kernel can write (device or mapped host memory)
   uint32_t wait_limit_ms;
   PartialState partial;
+  // Tile-stream split (dense calls without a caller-side partial chain): when non-null, the
+  // launch cuts the sequence of all (work item, K/V tile) pairs into one contiguous run per CTA
+  // instead of dealing whole items round-robin; items cut by a run boundary leave fp32 partials
+  // in `split_scratch` and the CTA whose piece finishes last merges them (see PieceWalk).
+  float* split_scratch;    // 2 slots of kSplitSlotFloats per CTA
+  int32_t* split_tickets;  // kSplitTicketsPerCta counters per CTA, zero between launches
+  int32_t split_runs;      // how many CTAs (the first ones) share the last round's items
   long long* trace;  // clock64 samples for timeline studies; used only by B200ATTN_TRACE builds
 };
+
+// Workspace of the tile-stream split, per CTA: two partial slots (a CTA has at most two cut
+// pieces, its first and its last), each holding a normalised fp32 O [256 rows][128] and its LSE
+// [256], and one arrival counter per (Q tile, epilogue warp).
+constexpr int kSplitSlotFloats = kItemRows * (kHeadDim + 1);
+constexpr int kSplitTicketsPerCta = kQTilesPerItem * 4;
+constexpr int kSplitMinPieceTiles = 8;  // a run boundary closer than this to an item boundary snaps to it
+constexpr size_t split_workspace_bytes(int ctas) {
+  return size_t(ctas) * (2 * size_t(kSplitSlotFloats) * sizeof(float) + kSplitTicketsPerCta * sizeof(int32_t));
+}
 
 // Launchers. Both return cudaGetLastError() of the launch.
 cudaError_t launch_fwd_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                           const FwdParams& p, int sm_count, cudaStream_t stream);
+// Grid and number of runs of a tile-stream split launch of `p` on `sm_count` SMs; grid == 0 if
+// splitting does not apply to `p` or would not shorten the launch.
+struct SplitPlan {
+  int grid, runs;
+};
+SplitPlan split_plan(const FwdParams& p, int sm_count);
 cudaError_t launch_fwd_serial(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                               const FwdParams& p, cudaStream_t stream);
 

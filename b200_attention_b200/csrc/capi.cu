@@ -303,6 +303,19 @@ int b200attn_forward(const b200attn_forward_args* a) {
 #if defined(B200ATTN_TRACE) || defined(B200ATTN_PROFILE)
   p.trace = g_trace_buffer;
 #endif
+  if (a->workspace != nullptr && a->kernel == B200ATTN_KERNEL_WARP_SPECIALIZED) {
+    if ((reinterpret_cast<uintptr_t>(a->workspace) & 15u) != 0)
+      return fail(B200ATTN_ERR_INVALID_ARGUMENT, "workspace must be 16-byte aligned");
+    if (a->workspace_bytes < split_workspace_bytes(st->sm_count))
+      return fail(B200ATTN_ERR_INVALID_ARGUMENT, "workspace is smaller than b200attn_workspace_bytes()");
+    const SplitPlan plan = split_plan(p, st->sm_count);
+    if (plan.grid > 0) {
+      p.split_runs = plan.runs;
+      p.split_scratch = static_cast<float*>(a->workspace);
+      p.split_tickets = reinterpret_cast<int32_t*>(static_cast<char*>(a->workspace) +
+                                                   size_t(st->sm_count) * 2 * kSplitSlotFloats * sizeof(float));
+    }
+  }
 
   CUtensorMap tq, tk, tv;
   const MapKey kq{a->q.ptr, a->q.stride_batch, a->q.stride_head, a->q.stride_row, a->batch, a->heads, a->len_q, device};
@@ -318,6 +331,16 @@ int b200attn_forward(const b200attn_forward_args* a) {
                             : launch_fwd_ws(tq, tk, tv, p, st->sm_count, stream);
   if (e != cudaSuccess) return fail_cuda("kernel launch", e);
   g_launches.fetch_add(1, std::memory_order_relaxed);
+  return B200ATTN_OK;
+}
+
+int b200attn_workspace_bytes(uint64_t* bytes) {
+  if (bytes == nullptr) return fail(B200ATTN_ERR_INVALID_ARGUMENT, "null argument");
+  int device = 0;
+  DeviceState* st = nullptr;
+  const int rc = get_device(&device, &st);
+  if (rc != 0) return rc;
+  *bytes = split_workspace_bytes(st->sm_count);
   return B200ATTN_OK;
 }
 

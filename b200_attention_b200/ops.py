@@ -17,6 +17,31 @@ from . import _native as N
 
 HEAD_DIM = 128
 
+# Workspaces of the tile-stream split, one per (device, stream): kernels on one stream run one
+# after the other and may share it, kernels on different streams may overlap and may not.
+_workspaces: dict = {}
+
+
+def workspace_for(device: torch.device, stream: torch.cuda.Stream) -> Optional[torch.Tensor]:
+    """The cached split workspace of (device, stream), allocated (zeroed) on first use; None while
+    the stream is being captured and nothing has been allocated for it yet."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream.cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None
+        size = C.c_uint64(0)
+        N.check(N.lib().b200attn_workspace_bytes(C.byref(size)))
+        with torch.cuda.stream(stream):
+            ws = torch.zeros(int(size.value), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def drop_workspaces() -> None:
+    """Forget every cached workspace (after a device-side timeout their counters may be stale)."""
+    _workspaces.clear()
+
 
 def _operand(t: torch.Tensor, layout: str) -> N.Operand:
     if layout == "bhld":
@@ -49,6 +74,7 @@ def attention(
     partial_merge: bool = False,
     partial_emit: bool = False,
     stream: Optional[torch.cuda.Stream] = None,
+    workspace="auto",
 ):
     """O = softmax(Q K^T * scale) V on the current CUDA stream.
 
@@ -59,6 +85,9 @@ def attention(
     (bottom-right aligned, needs Lk >= Lq).
     `partial=(o_fp32 [B,H,Lq,128], lse_fp32 [B,H,Lq])` with the two flags chains calls over K/V
     shards; see include/b200_attention.h.
+    `workspace`: "auto" (a zeroed device buffer cached per stream, which lets a dense call whose
+    work items do not fill the SMs evenly be cut into equal runs of K/V tiles), None (never
+    split), or a uint8 CUDA tensor of at least b200attn_workspace_bytes() zeroed bytes.
     """
     for name, t in (("q", q), ("k", k), ("v", v)):
         if not isinstance(t, torch.Tensor):
@@ -107,5 +136,13 @@ def attention(
         a.partial_emit = int(bool(partial_emit))
         s = stream if stream is not None else torch.cuda.current_stream(q.device)
         a.stream = s.cuda_stream
+        if isinstance(workspace, str):
+            if workspace != "auto":
+                raise ValueError("workspace must be 'auto', None or a uint8 CUDA tensor")
+            workspace = workspace_for(q.device, s) if (partial is None and not causal) else None
+        if workspace is not None:
+            if workspace.dtype != torch.uint8 or workspace.device != q.device or not workspace.is_contiguous():
+                raise RuntimeError("workspace must be a contiguous uint8 tensor on q's device")
+            a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
         N.check(N.lib().b200attn_forward(C.byref(a)))
     return (out, lse) if return_lse else out

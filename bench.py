@@ -431,8 +431,9 @@ def compare_with_k18(torch, ours, theirs, step_flops, stream, smclock, burst_n, 
     return out
 
 
-def configs_block(torch, ops, dev, stream, peaks, launches=8):
-    """The other benchmark configurations, a few launches each (inputs drawn on the GPU)."""
+def configs_block(torch, ops, dev, stream, peaks, launches=6):
+    """The other benchmark configurations, a few launches each (inputs drawn on the GPU), this
+    kernel and the reference kernel alternated so that neither always runs on the warmer GPU."""
     out = {}
     g = torch.Generator(device=dev).manual_seed(7)
     for name, layouts in CONFIG_SWEEP:
@@ -454,21 +455,25 @@ def configs_block(torch, ops, dev, stream, peaks, launches=8):
                 ops.attention(q, k, v, layout=layout, out=o)
 
             fl = flops(b, h, lq, lk)
-            for _ in range(3):
-                ours()
-            total, _, _ = time_launches(torch, ours, launches, stream)
-            ms = total / launches
+            theirs = k18_call(torch, q, k, v, layout)
+            arms = {"ours": ours} if theirs is None else {"ours": ours, "k18": theirs}
+            times = {arm: [] for arm in arms}
+            for order in (("ours", "k18"), ("k18", "ours")):   # each arm once first, once second
+                for arm in order:
+                    if arm not in arms:
+                        continue
+                    for _ in range(2):
+                        arms[arm]()
+                    total, _, _ = time_launches(torch, arms[arm], launches, stream)
+                    times[arm].append(total / launches)
+            ms = statistics.mean(times["ours"])
             entry = {"tflops": fl / (ms * 1e-3) / 1e12, "ms": ms}
             entry["pct_of_bf16_peak"] = 100.0 * entry["tflops"] / peaks["bf16_tflops"]
             nbytes = (2 * q.numel() + 2 * k.numel()) * 2
             entry["hbm_gbs_algorithmic"] = nbytes / (ms * 1e-3) / 1e9
             entry["pct_of_hbm_peak"] = 100.0 * entry["hbm_gbs_algorithmic"] / peaks["hbm_gbs"]
-            theirs = k18_call(torch, q, k, v, layout)
             if theirs is not None:
-                for _ in range(3):
-                    theirs()
-                total, _, _ = time_launches(torch, theirs, launches, stream)
-                entry["k18_tflops"] = fl / (total / launches * 1e-3) / 1e12
+                entry["k18_tflops"] = fl / (statistics.mean(times["k18"]) * 1e-3) / 1e12
                 entry["ratio_to_k18"] = entry["tflops"] / entry["k18_tflops"]
             out[f"{name}_{layout}"] = {k_: (round(v_, 3) if isinstance(v_, float) else v_)
                                        for k_, v_ in entry.items()}

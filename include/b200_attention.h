@@ -97,10 +97,25 @@ typedef struct b200attn_forward_args {
    *                  0 means heads_kv == heads. */
   int32_t causal;
   int32_t heads_kv;
+  /* Optional workspace for the tile-stream split (no counterpart in the reference, whose
+   * scheduler deals whole 256-row work items round-robin, 18_tma_l2_promotion.cu:1039-1046).
+   * With at least b200attn_workspace_bytes() of ZEROED, 16-byte aligned device memory here, a
+   * dense call whose work items do not fill the SMs evenly (e.g. 256 items on 148 SMs) is cut
+   * into one equal run of K/V tiles per SM instead; work items cut by a run boundary are merged
+   * in the kernel through this memory (fp32 partial O and LSE, arrival counters that return to
+   * zero). The call decides by itself whether splitting pays; results are the same up to
+   * rounding. The memory may be reused by later calls on the SAME stream; calls whose kernels
+   * can overlap (other streams) need workspaces of their own. After a call that ended in
+   * B200ATTN_ERR_DEVICE_TIMEOUT, zero it again. NULL: never split. */
+  void* workspace;
+  uint64_t workspace_bytes;
 } b200attn_forward_args;
 
 /* Asynchronous on args->stream. The device that is current when the call is made is used. */
 B200ATTN_API int b200attn_forward(const b200attn_forward_args* args);
+
+/* Size of b200attn_forward_args.workspace for the current device (depends on its SM count). */
+B200ATTN_API int b200attn_workspace_bytes(uint64_t* bytes);
 
 /* Q [batch_heads, len_q, 128], K/V [batch_heads, len_kv, 128], O like Q; all contiguous bf16.
  * Unlike the reference launcher there is no len_q % 256 / len_kv % 128 restriction. */

@@ -39,9 +39,9 @@ def test_version_and_status_strings(native_built):
 
 def test_struct_layout_matches_header(native_built):
     # 6 x 4 bytes, 4 operands of 32 bytes, lse ptr, scale + kernel, 2 ptrs, 2 ints, stream,
-    # causal + heads_kv
+    # causal + heads_kv, workspace pointer + size
     assert C.sizeof(N.Operand) == 32
-    assert C.sizeof(N.ForwardArgs) == 24 + 4 * 32 + 8 + 8 + 16 + 8 + 8 + 8
+    assert C.sizeof(N.ForwardArgs) == 24 + 4 * 32 + 8 + 8 + 16 + 8 + 8 + 8 + 16
 
 
 def _args(**over):

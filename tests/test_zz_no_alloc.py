@@ -83,3 +83,29 @@ def test_no_alloc_entry_single_chunk_and_limit(native_built):
     rc = lib.b200attn_forward_kv_split_noalloc(C.byref(_args(N, big, k[:, :1], v[:, :1], big, big_lse)), 2)
     assert rc == N.STATUS_UNSUPPORTED
     assert b"16384" in lib.b200attn_last_error()
+
+
+def test_no_alloc_entry_on_two_devices(native_built):
+    """Every GPU that loads the library has its own copy of the built-in array, and the entry point
+    looks the array's address up once per device with that device current: calls on a second GPU
+    must land in that GPU's copy. (Skipped with fewer than two GPUs.)"""
+    if not torch.cuda.is_available():
+        pytest.fail("this test needs a CUDA device")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from b200_attention_b200 import _native as N
+
+    lib = N.lib()
+    b, h, lq, lk = 1, 2, 256, 1024
+    for dev in (1, 0, 1):
+        with torch.cuda.device(dev):
+            q, k, v = (O.to_bhld(t).cuda() for t in O.make_inputs_benchmark(b, h, lq, lk, seed=30 + dev))
+            o_ref, o_new = torch.empty_like(q), torch.empty_like(q)
+            lse_ref = torch.empty(b, h, lq, dtype=torch.float32, device="cuda")
+            lse_new = torch.empty_like(lse_ref)
+            N.check(lib.b200attn_forward(C.byref(_args(N, q, k, v, o_ref, lse_ref))))
+            N.check(lib.b200attn_forward_kv_split_noalloc(C.byref(_args(N, q, k, v, o_new, lse_new)), 2))
+            torch.cuda.synchronize()
+            N.device_check()
+            N.check(lib.b200attn_forward_kv_split_noalloc(C.byref(_args(N, q, k, v, o_new, lse_new)), 0))
+            O.assert_within_contract(O.compare(o_new, o_ref, lse_new, lse_ref))
