@@ -217,7 +217,6 @@ class RingAttention:
                 self._out = torch.empty_like(q)
             out = self._out
         main = torch.cuda.current_stream(dev)
-        side = self._copy_stream
         order = ring_schedule(self.world, self.rank)
         flags = chain_flags(self.world)
         if self._events is None or len(self._events[0]) != self.world:
@@ -237,6 +236,7 @@ class RingAttention:
             self._ready.synchronize()
             if self._any_rank(not self._peers or self._bound != key):
                 self.bind(k_local, v_local)
+        side = self._copy_stream
 
         def start_pull(step: int) -> None:
             buf = self._staging[step % 2]
