@@ -22,29 +22,52 @@ if TYPE_CHECKING:
 
 HEAD_DIM = 128
 
-_STATS_LOCK = threading.Lock()
-_TOTAL_CALLS = 0
-_SIGNATURES: Counter = Counter()
-_UNIQUE_INPUTS: set = set()
+
+class _CallLog:
+    """Process-wide record of successful attention calls. What the reference's CLI reads from it
+    (capstone-project/src/ltx_sm100/cli.py:167-208) is the contract: the three keys of
+    `snapshot()` and the text of a signature."""
+
+    def __init__(self) -> None:
+        self._guard = threading.Lock()
+        self._calls = 0
+        self._by_signature: Counter = Counter()
+        self._layouts: set = set()
+
+    def clear(self) -> None:
+        with self._guard:
+            self._calls = 0
+            self._by_signature.clear()
+            self._layouts.clear()
+
+    def add(self, tensors, dims) -> None:
+        query = tensors[0]
+        signature = ("B={0},Lq={1},Lkv={2},H={3},D={4},".format(*dims)
+                     + f"dtype={query.dtype},device={query.device}")
+        layout = "; ".join(f"{name}_shape={tuple(t.shape)} {name}_stride={tuple(t.stride())}"
+                           for name, t in zip("qkv", tensors))
+        with self._guard:
+            self._calls += 1
+            self._by_signature[signature] += 1
+            self._layouts.add(layout)
+
+    def snapshot(self) -> dict[str, Any]:
+        with self._guard:
+            return {"total_calls": self._calls, "signatures": dict(self._by_signature),
+                    "unique_inputs": sorted(self._layouts)}
+
+
+_LOG = _CallLog()
 
 
 def reset_stats() -> None:
     """Reset the process-wide statistics of successful attention calls."""
-    global _TOTAL_CALLS
-    with _STATS_LOCK:
-        _TOTAL_CALLS = 0
-        _SIGNATURES.clear()
-        _UNIQUE_INPUTS.clear()
+    _LOG.clear()
 
 
 def get_stats() -> dict[str, Any]:
     """JSON-serialisable snapshot: total_calls, signatures, unique_inputs."""
-    with _STATS_LOCK:
-        return {
-            "total_calls": _TOTAL_CALLS,
-            "signatures": dict(_SIGNATURES),
-            "unique_inputs": sorted(_UNIQUE_INPUTS),
-        }
+    return _LOG.snapshot()
 
 
 def ensure_loaded() -> None:
@@ -54,69 +77,57 @@ def ensure_loaded() -> None:
     _native.lib()
 
 
-def _validate_inputs(query, key, value, heads, mask):
-    # Order matters: the mask check comes first so that it needs neither torch nor CUDA.
+def _refuse(kind, text):
+    raise kind("B200Attention " + text)
+
+
+def _check_call(query, key, value, heads, mask):
+    """The rules of the reference callable (capstone-project/src/ltx_sm100/backend.py:64-141), in an
+    order that keeps its promise that a mask is refused before torch or CUDA are touched, minus its
+    length rules (no multiple-of-256 / multiple-of-128 requirement here). Returns
+    (batch, len_q, len_kv, head_dim). The wording callers match on is kept: "unmasked attention
+    only", "BF16", "head dimension 128"."""
     if mask is not None:
-        raise RuntimeError("B200Attention supports dense, unmasked attention only.")
+        _refuse(RuntimeError, "supports dense, unmasked attention only.")
     import torch
 
-    if not all(isinstance(t, torch.Tensor) for t in (query, key, value)):
-        raise TypeError("B200Attention requires query, key, and value to be torch.Tensor instances.")
-    if not isinstance(heads, int) or isinstance(heads, bool) or heads <= 0:
-        raise ValueError(f"B200Attention requires a positive integer head count, got {heads!r}.")
-    if not (query.is_cuda and key.is_cuda and value.is_cuda):
-        raise RuntimeError("B200Attention requires CUDA query/key/value tensors.")
-    if query.device != key.device or query.device != value.device:
-        raise RuntimeError("B200Attention requires query/key/value on the same CUDA device.")
-    capability = torch.cuda.get_device_capability(query.device)
-    if capability != (10, 0):
-        raise RuntimeError(
-            "B200Attention requires an NVIDIA B200-class SM100 GPU (compute capability 10.0), "
-            f"got {capability[0]}.{capability[1]}.")
-    if any(t.dtype != torch.bfloat16 for t in (query, key, value)):
-        raise RuntimeError(
-            "B200Attention requires BF16 query/key/value tensors; "
-            f"got query={query.dtype}, key={key.dtype}, value={value.dtype}.")
-    if query.ndim != 3 or key.ndim != 3 or value.ndim != 3:
-        raise RuntimeError(
-            "B200Attention expects query/key/value shaped [B, T, H*D]; "
-            f"got query={tuple(query.shape)}, key={tuple(key.shape)}, value={tuple(value.shape)}.")
-    batch, query_length, hidden = query.shape
-    if batch <= 0 or query_length <= 0 or key.shape[1] <= 0:
-        raise RuntimeError("B200Attention requires non-empty batch and sequence dimensions.")
+    qkv = (query, key, value)
+    if not all(isinstance(t, torch.Tensor) for t in qkv):
+        _refuse(TypeError, "requires query, key, and value to be torch.Tensor instances.")
+    if isinstance(heads, bool) or not isinstance(heads, int) or heads <= 0:
+        _refuse(ValueError, f"requires a positive integer head count, got {heads!r}.")
+    if not all(t.is_cuda for t in qkv):
+        _refuse(RuntimeError, "requires CUDA query/key/value tensors.")
+    if len({t.device for t in qkv}) != 1:
+        _refuse(RuntimeError, "requires query/key/value on the same CUDA device.")
+    major, minor = torch.cuda.get_device_capability(query.device)
+    if (major, minor) != (10, 0):
+        _refuse(RuntimeError, "requires an NVIDIA B200-class SM100 GPU (compute capability 10.0), "
+                              f"got {major}.{minor}.")
+    shapes = ", ".join(f"{n}={tuple(t.shape)}" for n, t in zip(("query", "key", "value"), qkv))
+    if any(t.dtype != torch.bfloat16 for t in qkv):
+        _refuse(RuntimeError, "requires BF16 query/key/value tensors; got "
+                + ", ".join(f"{n}={t.dtype}" for n, t in zip(("query", "key", "value"), qkv)) + ".")
+    if any(t.ndim != 3 for t in qkv):
+        _refuse(RuntimeError, f"expects query/key/value shaped [B, T, H*D]; got {shapes}.")
+    batch, len_q, hidden = query.shape
+    len_kv = key.shape[1]
+    if min(batch, len_q, len_kv) <= 0:
+        _refuse(RuntimeError, "requires non-empty batch and sequence dimensions.")
     if key.shape[0] != batch or value.shape[0] != batch:
-        raise RuntimeError(
-            "B200Attention requires matching query/key/value batch dimensions; "
-            f"got query={batch}, key={key.shape[0]}, value={value.shape[0]}.")
-    if value.shape[1] != key.shape[1]:
-        raise RuntimeError(
-            "B200Attention requires matching key/value sequence lengths; "
-            f"got key={key.shape[1]}, value={value.shape[1]}.")
+        _refuse(RuntimeError, f"requires matching query/key/value batch dimensions; got {shapes}.")
+    if value.shape[1] != len_kv:
+        _refuse(RuntimeError, f"requires matching key/value sequence lengths; got {shapes}.")
     if key.shape[2] != hidden or value.shape[2] != hidden:
-        raise RuntimeError(
-            "B200Attention requires matching query/key/value hidden dimensions; "
-            f"got query={hidden}, key={key.shape[2]}, value={value.shape[2]}.")
-    if hidden % heads != 0:
-        raise RuntimeError(f"B200Attention cannot split hidden dimension {hidden} across {heads} heads.")
-    head_dim = hidden // heads
+        _refuse(RuntimeError, f"requires matching query/key/value hidden dimensions; got {shapes}.")
+    head_dim, rest = divmod(hidden, heads)
+    if rest:
+        _refuse(RuntimeError, f"cannot split hidden dimension {hidden} across {heads} heads.")
     if head_dim != HEAD_DIM:
-        raise RuntimeError(f"B200Attention supports head dimension 128 only, got {head_dim}.")
-    if max(batch * heads, query_length, key.shape[1]) > 2**31 - 1:
-        raise RuntimeError("B200Attention dimensions exceed 32-bit integer limits.")
-    return batch, query_length, key.shape[1], head_dim
-
-
-def _record_success(query, key, value, *, batch, query_length, key_value_length, heads, head_dim):
-    global _TOTAL_CALLS
-    signature = (f"B={batch},Lq={query_length},Lkv={key_value_length},H={heads},D={head_dim},"
-                 f"dtype={query.dtype},device={query.device}")
-    input_record = (f"q_shape={tuple(query.shape)} q_stride={tuple(query.stride())}; "
-                    f"k_shape={tuple(key.shape)} k_stride={tuple(key.stride())}; "
-                    f"v_shape={tuple(value.shape)} v_stride={tuple(value.stride())}")
-    with _STATS_LOCK:
-        _TOTAL_CALLS += 1
-        _SIGNATURES[signature] += 1
-        _UNIQUE_INPUTS.add(input_record)
+        _refuse(RuntimeError, f"supports head dimension 128 only, got {head_dim}.")
+    if max(batch * heads, len_q, len_kv) >= 2**31:
+        _refuse(RuntimeError, "dimensions exceed 32-bit integer limits.")
+    return batch, len_q, len_kv, head_dim
 
 
 class B200Attention:
@@ -129,7 +140,7 @@ class B200Attention:
         self._loaded = False
 
     def __call__(self, query, key, value, heads: int, mask=None):
-        batch, lq, lk, head_dim = _validate_inputs(query, key, value, heads, mask)
+        batch, lq, lk, head_dim = _check_call(query, key, value, heads, mask)
         if not self._loaded:
             ensure_loaded()
             self._loaded = True
@@ -147,8 +158,7 @@ class B200Attention:
         q4, k4, v4 = as_bshd(query), as_bshd(key), as_bshd(value)
         out = ops.attention(q4, k4, v4, layout="bshd", softmax_scale=self._softmax_scale)
         output = out.view(batch, lq, heads * head_dim)
-        _record_success(query, key, value, batch=batch, query_length=lq, key_value_length=lk,
-                        heads=heads, head_dim=head_dim)
+        _LOG.add((query, key, value), (batch, lq, lk, heads, head_dim))
         return output
 
 

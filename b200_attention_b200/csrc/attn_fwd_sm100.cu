@@ -350,12 +350,21 @@ enum WsBarrier : int {
   kNumWsBarriers = 24
 };
 
+struct Piece {
+  int item, t0, t1;  // K/V tiles [t0, t1) of work item `item`
+};
+constexpr int kMaxRunPieces = 4;  // a run is shorter than one item plus a snap: two pieces, four slots
+
 struct alignas(16) WsAux {
   uint64_t bar[kNumWsBarriers];
   float row_max[kQTilesPerItem][kBlockM];
   float row_sum[kQTilesPerItem][kBlockM];
   uint32_t tmem_base;
   uint32_t abort_flag;
+  // tile-stream split: this CTA's pieces of the last round, worked out once by thread 0
+  int32_t run_pieces;
+  int32_t whole_items;  // items [0, whole_items) are dealt round-robin as whole items
+  Piece run_piece[kMaxRunPieces];
 };
 
 constexpr int kWsSmemBytes = kQTilesPerItem * kTileBytes + kPairSlots * kPairBytes + int(sizeof(WsAux));
@@ -447,41 +456,17 @@ __device__ __forceinline__ int split_owner(const FwdParams& p, int u, int grid) 
   return c;
 }
 
-struct Piece {
-  int item, t0, t1;  // K/V tiles [t0, t1) of work item `item`
-};
-
-// Hands out a CTA's pieces one by one. Between two pieces only (item, u, u_end) are live.
+// Hands out a CTA's pieces one by one. Without splitting that is the plain round-robin walk over
+// whole items, with nothing but the item number live between two pieces.
 template <bool kSplit>
-struct PieceWalk {
-  int item;      // the next whole item of the full rounds
-  int u, u_end;  // kSplit: first unit of the next piece of the last round, end of this CTA's run
+struct PieceWalk;
 
-  __device__ __forceinline__ explicit PieceWalk(const FwdParams& p) {
-    item = int(blockIdx.x);
-    if (kSplit) {
-      u = split_cut(p, int(blockIdx.x), int(gridDim.x));
-      u_end = split_cut(p, int(blockIdx.x) + 1, int(gridDim.x));
-    } else {
-      u = u_end = 0;
-    }
-  }
-  // The next piece, if there is one. The run through the last round's items comes first and the
-  // whole items of the full rounds after it: the merge of a cut item (done by the epilogue warps
-  // of whichever CTA finishes its piece last) then overlaps that CTA's remaining whole items
-  // instead of standing at the end of the launch.
+template <>
+struct PieceWalk<false> {
+  int item;
+  __device__ __forceinline__ PieceWalk(const FwdParams&, const WsAux*) : item(int(blockIdx.x)) {}
   __device__ __forceinline__ bool take(const FwdParams& p, Piece& out) {
-    const int whole_items = kSplit ? split_first_item(p, int(gridDim.x)) : p.total_items;
-    if (kSplit && u < u_end) {
-      const int k = u / p.kv_tiles;
-      out.item = whole_items + k;
-      out.t0 = u - k * p.kv_tiles;
-      const int left = u_end - u;
-      out.t1 = (left < p.kv_tiles - out.t0) ? out.t0 + left : p.kv_tiles;
-      u += out.t1 - out.t0;
-      return true;
-    }
-    if (item >= whole_items) return false;
+    if (item >= p.total_items) return false;
     out.item = item;
     out.t0 = 0;
     out.t1 = p.kv_tiles;
@@ -489,6 +474,53 @@ struct PieceWalk {
     return true;
   }
 };
+
+// With splitting: the CTA's run through the last round's items comes first (its pieces were put
+// into shared memory at start-up) and the whole items of the full rounds after it: the merge of a
+// cut item (done by the epilogue warps of whichever CTA finishes its piece last) then overlaps
+// that CTA's remaining whole items instead of standing at the end of the launch. Between two
+// pieces only a counter is live, which matters to the warps that run on 48 registers.
+template <>
+struct PieceWalk<true> {
+  const WsAux* aux;
+  int k;
+  __device__ __forceinline__ PieceWalk(const FwdParams&, const WsAux* a) : aux(a), k(0) {}
+  __device__ __forceinline__ bool take(const FwdParams& p, Piece& out) {
+    const int n = aux->run_pieces;
+    if (k < n) {
+      out = aux->run_piece[k];
+    } else {
+      const int item = int(blockIdx.x) + (k - n) * int(gridDim.x);
+      if (item >= aux->whole_items) return false;
+      out.item = item;
+      out.t0 = 0;
+      out.t1 = p.kv_tiles;
+    }
+    ++k;
+    return true;
+  }
+};
+
+// Thread 0, before the roles start: this CTA's run through the last round, as pieces.
+__device__ __forceinline__ void plan_run(const FwdParams& p, WsAux* aux) {
+  const int grid = int(gridDim.x);
+  const int whole_items = split_first_item(p, grid);
+  int u = split_cut(p, int(blockIdx.x), grid);
+  const int u_end = split_cut(p, int(blockIdx.x) + 1, grid);
+  int n = 0;
+  while (u < u_end && n < kMaxRunPieces) {
+    const int k = u / p.kv_tiles;
+    Piece pc;
+    pc.item = whole_items + k;
+    pc.t0 = u - k * p.kv_tiles;
+    const int left = u_end - u;
+    pc.t1 = (left < p.kv_tiles - pc.t0) ? pc.t0 + left : p.kv_tiles;
+    aux->run_piece[n++] = pc;
+    u += pc.t1 - pc.t0;
+  }
+  aux->run_pieces = n;
+  aux->whole_items = whole_items;
+}
 
 // ---- TMA producer -------------------------------------------------------------------------
 __device__ __forceinline__ void load_tile(uint32_t lead, uint32_t dst, const CUtensorMap* map,
@@ -499,9 +531,9 @@ __device__ __forceinline__ void load_tile(uint32_t lead, uint32_t dst, const CUt
 }
 
 template <bool kCausal, bool kSplit>
-__device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CUtensorMap* tk,
-                             const CUtensorMap* tv, uint32_t smem_q, uint32_t smem_kv,
-                             uint32_t bar0, uint32_t lead, WaitCtx& w) {
+__device__ void ws_load_role(const FwdParams& p, const WsAux* aux, const CUtensorMap* tq,
+                             const CUtensorMap* tk, const CUtensorMap* tv, uint32_t smem_q,
+                             uint32_t smem_kv, uint32_t bar0, uint32_t lead, WaitCtx& w) {
   // Run by the whole warp with uniform control flow; `lead` marks the one lane that issues.
   //
   // K/V travel in pairs: pair j holds V of tile j-1 and K of tile j (tiles numbered through all
@@ -540,7 +572,7 @@ __device__ void ws_load_role(const FwdParams& p, const CUtensorMap* tq, const CU
   };
 
   bool first = true;
-  PieceWalk<kSplit> pw(p);
+  PieceWalk<kSplit> pw(p, aux);
   Piece pc;
   while (ok && pw.take(p, pc)) {
     const int item = pc.item;
@@ -697,8 +729,8 @@ __device__ void ws_mma_role_causal(const FwdParams& p, uint32_t smem_q, uint32_t
 }
 
 template <bool kCausal, bool kSplit>
-__device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_kv, uint32_t bar0,
-                            uint32_t tmem_base, uint32_t lead, WaitCtx& w) {
+__device__ void ws_mma_role(const FwdParams& p, const WsAux* aux, uint32_t smem_q, uint32_t smem_kv,
+                            uint32_t bar0, uint32_t tmem_base, uint32_t lead, WaitCtx& w) {
   if (kCausal) {
     ws_mma_role_causal(p, smem_q, smem_kv, bar0, tmem_base, lead, w);
     return;
@@ -717,11 +749,11 @@ __device__ void ws_mma_role(const FwdParams& p, uint32_t smem_q, uint32_t smem_k
 
   PROF_DECL(8);  // 0 other, 1 wait pair, 3 wait P (+O_FREE), 4 issue PV, 5 issue QK, 6 commits
 
-  PieceWalk<kSplit> pw(p);
+  PieceWalk<kSplit> pw(p, aux);
   Piece pc;
   while (ok && pw.take(p, pc)) {
     const int item = pc.item;
-    const int T = pc.t1 - pc.t0;
+    const int T = kSplit ? pc.t1 - pc.t0 : p.kv_tiles;
     w.item = item;
     w.tile = 0;
     // ---- first scores of the piece for both Q tiles
@@ -869,7 +901,7 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
   uint32_t fin_free_parity = 1;  // passes on the fresh barrier: nothing to consume yet
   PROF_DECL(8);  // 0 other, 1 wait S, 2 TMEM load, 3 exponentials + check, 4 store + signal
 
-  PieceWalk<kSplit> pw(p);
+  PieceWalk<kSplit> pw(p, aux);
   Piece pc;
   while (pw.take(p, pc)) {
     const int item = pc.item;
@@ -1117,7 +1149,7 @@ __device__ void ws_epilogue_role(const FwdParams& p, WsAux* aux, uint32_t bar0, 
   const int r = warp_in_group * 32 + lane;
   uint32_t fin_parity = 0;
 
-  PieceWalk<kSplit> pw(p);
+  PieceWalk<kSplit> pw(p, aux);
   Piece pc;
   while (pw.take(p, pc)) {
     const int item = pc.item;
@@ -1220,6 +1252,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
       }
       mbar_init_fence();
       fence_proxy_async_smem();
+      if (kSplit) plan_run(p, aux);
     }
   }
   if (misaligned) return;
@@ -1242,7 +1275,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
     reg_shrink<kRegsOther>();
     const uint32_t lead = (lane == 0) ? 1u : 0u;
     if (warp == 12) {
-      ws_mma_role<kCausal, kSplit>(p, smem_q, smem_kv, bar0, tmem_base, lead, w);
+      ws_mma_role<kCausal, kSplit>(p, aux, smem_q, smem_kv, bar0, tmem_base, lead, w);
     } else if (warp == 13) {
       if (lead) {
         tma_prefetch_desc(&tmap_q);
@@ -1250,7 +1283,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
         tma_prefetch_desc(&tmap_v);
       }
       __syncwarp();
-        ws_load_role<kCausal, kSplit>(p, &tmap_q, &tmap_k, &tmap_v, smem_q, smem_kv, bar0, lead, w);
+        ws_load_role<kCausal, kSplit>(p, aux, &tmap_q, &tmap_k, &tmap_v, smem_q, smem_kv, bar0, lead, w);
     }
     __syncwarp();
   }

@@ -67,7 +67,7 @@ struct FwdParams {
 // [256], and one arrival counter per (Q tile, epilogue warp).
 constexpr int kSplitSlotFloats = kItemRows * (kHeadDim + 1);
 constexpr int kSplitTicketsPerCta = kQTilesPerItem * 4;
-constexpr int kSplitMinPieceTiles = 8;  // a run boundary closer than this to an item boundary snaps to it
+constexpr int kSplitMinPieceTiles = 4;  // a run boundary closer than this to an item boundary snaps to it
 constexpr size_t split_workspace_bytes(int ctas) {
   return size_t(ctas) * (2 * size_t(kSplitSlotFloats) * sizeof(float) + kSplitTicketsPerCta * sizeof(int32_t));
 }

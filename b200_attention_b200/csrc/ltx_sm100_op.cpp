@@ -5,7 +5,10 @@
 // at the built libltx_sm100_attention.so to use it without touching the capstone code.
 //
 // Differences, all relaxations: query length need not be a multiple of 256 and key/value
-// length need not be a multiple of 128.
+// length need not be a multiple of 128. The argument checks below restate the reference
+// binding's own list (binding.cpp:31-76: device, dtype, rank, head dimension, matching batch and
+// K/V shapes, contiguity, sizes within int), in its order and with its message texts, because
+// callers of the op match on those messages.
 
 #include <ATen/ATen.h>
 #include <c10/cuda/CUDAGuard.h>

@@ -556,6 +556,22 @@ def run_ours(args, rank, local_rank, world):
     kernel_ms = statistics.mean(per_launch)
     achieved = rank_flops / (kernel_ms * 1e-3) / 1e12
     burst = regime(total_ms, args.steps, job_flops, burst_mhz)
+    if args.only_timed:
+        # profiling aid: the contract's region only (plus, if asked, a few launches of the reference
+        # kernel for a counter-by-counter comparison under the same profiler)
+        if rank == 0 and args.k18_launches > 0:
+            theirs = k18_call(torch, q, k, v, layout)
+            for _ in range(args.k18_launches if theirs is not None else 0):
+                theirs()
+            torch.cuda.synchronize(dev)
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world,
+                              "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+                              "burst": burst, "gpu_launches": int(launches), "only_timed": True,
+                              "config": workload_config(args.workload, world)}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- the power-capped regime: >= 0.5 s of warm-up, >= 1 s timed, clocks sampled over it
     sampler = ClockSampler(physical_gpu_index(local_rank))
@@ -1038,6 +1054,10 @@ def main():
     ap.add_argument("--cpu-budget", type=float, default=12.0)
     ap.add_argument("--sustain-s", type=float, default=1.0, help="length of the sustained timed regions")
     ap.add_argument("--k18-rounds", type=int, default=2)
+    ap.add_argument("--only-timed", action="store_true",
+                    help="profiling aid: warm-up and the timed launches only, then stop")
+    ap.add_argument("--k18-launches", type=int, default=0,
+                    help="with --only-timed: also launch the reference kernel this many times")
     args = ap.parse_args()
     args.steps_given, args.warmup_given = args.steps is not None, args.warmup is not None
     args.steps = 100 if args.steps is None else args.steps

@@ -79,8 +79,8 @@ def test_stats_signature_format():
     q = torch.zeros(1, 512, 256, dtype=torch.bfloat16)
     k = torch.zeros(1, 128, 256, dtype=torch.bfloat16)
     backend.reset_stats()
-    backend._record_success(q, k, k, batch=1, query_length=512, key_value_length=128, heads=2, head_dim=128)
-    backend._record_success(q, k, k, batch=1, query_length=512, key_value_length=128, heads=2, head_dim=128)
+    backend._LOG.add((q, k, k), (1, 512, 128, 2, 128))
+    backend._LOG.add((q, k, k), (1, 512, 128, 2, 128))
     stats = backend.get_stats()
     assert stats["total_calls"] == 2
     assert stats["signatures"] == {"B=1,Lq=512,Lkv=128,H=2,D=128,dtype=torch.bfloat16,device=cpu": 2}
