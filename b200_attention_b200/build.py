@@ -60,10 +60,12 @@ def _run(cmd, verbose: bool) -> None:
         print(proc.stdout, proc.stderr, flush=True)
 
 
-def build_core(force: bool = False, verbose: bool = False, defines: tuple[str, ...] = ()) -> Path:
-    """Kernels + C ABI -> libb200attn.so (links the CUDA runtime statically)."""
+def build_core(force: bool = False, verbose: bool = False, defines: tuple[str, ...] = (),
+               name: str = "libb200attn.so") -> Path:
+    """Kernels + C ABI -> libb200attn.so (links the CUDA runtime statically). `defines` and `name`
+    build an instrumented variant beside it (see role_budget.py)."""
     LIB.mkdir(exist_ok=True)
-    out = LIB / "libb200attn.so"
+    out = LIB / name
     flags = ["-std=c++17", "-O3", "-lineinfo", *ARCH_FLAGS, "-Xcompiler", "-fPIC,-fvisibility=hidden",
              "-Xptxas", "-v", *[f"-D{d}" for d in defines]]
     digest = _digest(CORE_SOURCES + CORE_HEADERS, " ".join(flags))

@@ -248,7 +248,7 @@ __device__ __forceinline__ RowOut make_row_out(const FwdParams& p, int b, int h,
 template <class AfterLastLd>
 __device__ __forceinline__ void store_row(const RowOut& r, uint32_t o_tmem_row,
                                           AfterLastLd after_last_ld) {
-  constexpr int kChunk = 16;  // columns per TMEM read: keeps the epilogue inside 80 registers
+  constexpr int kChunk = 16;  // columns per TMEM read: keeps the epilogue inside 64 registers
 #pragma unroll 1
   for (int c = 0; c < kHeadDim / kChunk; ++c) {
     uint32_t acc[kChunk];
@@ -331,8 +331,8 @@ constexpr int kPairSlots = 2;                 // ring of (V, K) pairs
 constexpr int kPairBytes = 2 * kTileBytes;    // V tile, then K tile
 constexpr int kWsThreads = 512;
 constexpr int kRegsSoftmax = 192;
-constexpr int kRegsEpilogue = 80;
-constexpr int kRegsOther = 48;
+constexpr int kRegsEpilogue = 64;
+constexpr int kRegsOther = 64;
 
 enum WsBarrier : int {
   kBarQFull = 0,    // +q   TMA -> MMA       Q tile q landed
@@ -479,7 +479,7 @@ struct PieceWalk<false> {
 // into shared memory at start-up) and the whole items of the full rounds after it: the merge of a
 // cut item (done by the epilogue warps of whichever CTA finishes its piece last) then overlaps
 // that CTA's remaining whole items instead of standing at the end of the launch. Between two
-// pieces only a counter is live, which matters to the warps that run on 48 registers.
+// pieces only a counter is live, which matters to the warps that run on 64 registers.
 template <>
 struct PieceWalk<true> {
   const WsAux* aux;
