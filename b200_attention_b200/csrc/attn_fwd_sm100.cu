@@ -4,14 +4,18 @@
 //
 // Two kernels share the operand layout, descriptors and epilogue:
 //
-//   attn_fwd_ws_kernel      the production kernel (a template on the causal mask). Persistent
+//   attn_fwd_ws_kernel      the production kernel (a template on the causal mask and on how
+//                           work is dealt: whole 256-row work items round-robin, or with the
+//                           last, partly filled round cut into equal runs of K/V tiles whose cut
+//                           items are merged through a caller-provided workspace). Persistent
 //                           CTAs (one per SM), 16 warps:
 //                             warps 0-3   softmax for Q tile 0 (one query row per thread); also
 //                                         the rare rebase of the O accumulator when a row's
 //                                         reference maximum has to move
 //                             warps 4-7   softmax for Q tile 1
 //                             warps 8-11  epilogue: normalise, merge with a previous partial,
-//                                         store O / LSE
+//                                         store O / LSE; partial stores, tickets and merges of
+//                                         cut work items
 //                             warp 12     issues every tcgen05.mma
 //                             warp 13     issues every TMA load
 //                             warps 14-15 only give their registers away
@@ -1192,13 +1196,19 @@ __device__ void ws_epilogue_role(const FwdParams& p, WsAux* aux, uint32_t bar0, 
         if (lane == 0) mbar_arrive(bar(kBarOFree + q));
       });
     }
-    // Both accumulators have been handed back: the tickets and (for the piece that finishes last)
-    // the merge now run beside the CTA's next piece.
+    // Tickets and merges of the run's cut pieces wait until the run's last piece has handed both
+    // accumulators back: they then run beside the CTA's whole items (or, with none, at the end)
+    // and never between two short pieces, where they would hold up the next hand-back.
     if constexpr (kSplit) {
-      if (cut) {
-        for (int q = 0; q < kQTilesPerItem; ++q) {
-          split_merge_rows(p, pc, c, q, warp_in_group, lane);
-          __syncwarp();
+      if (pw.k == aux->run_pieces) {
+        for (int j = 0; j < aux->run_pieces; ++j) {
+          const Piece done = aux->run_piece[j];
+          if (done.t0 == 0 && done.t1 == p.kv_tiles) continue;
+          const ItemCoord dc = decode_item<kCausal>(p, done.item);
+          for (int q = 0; q < kQTilesPerItem; ++q) {
+            split_merge_rows(p, done, dc, q, warp_in_group, lane);
+            __syncwarp();
+          }
         }
       }
     }

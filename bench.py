@@ -431,7 +431,7 @@ def compare_with_k18(torch, ours, theirs, step_flops, stream, smclock, burst_n, 
     return out
 
 
-def configs_block(torch, ops, dev, stream, peaks, launches=6):
+def configs_block(torch, ops, dev, stream, peaks, launches=10):
     """The other benchmark configurations, a few launches each (inputs drawn on the GPU), this
     kernel and the reference kernel alternated so that neither always runs on the warmer GPU."""
     out = {}
@@ -458,11 +458,13 @@ def configs_block(torch, ops, dev, stream, peaks, launches=6):
             theirs = k18_call(torch, q, k, v, layout)
             arms = {"ours": ours} if theirs is None else {"ours": ours, "k18": theirs}
             times = {arm: [] for arm in arms}
+            torch.cuda.synchronize(dev)
+            time.sleep(0.3)   # every configuration starts from the same short idle
             for order in (("ours", "k18"), ("k18", "ours")):   # each arm once first, once second
                 for arm in order:
                     if arm not in arms:
                         continue
-                    for _ in range(2):
+                    for _ in range(3):
                         arms[arm]()
                     total, _, _ = time_launches(torch, arms[arm], launches, stream)
                     times[arm].append(total / launches)
