@@ -33,6 +33,7 @@ NOALLOC_MAX_ROWS = 16384
 EXPORTED_SYMBOLS = (
     "b200attn_forward",
     "b200attn_workspace_bytes",
+    "b200attn_split_layout",
     "b200attn_bhld_launch",
     "b200attn_bshd_launch",
     "b200attn_forward_kv_split_noalloc",
@@ -108,6 +109,8 @@ def lib() -> C.CDLL:
         handle.b200attn_forward.restype = C.c_int
         handle.b200attn_workspace_bytes.argtypes = [C.POINTER(C.c_uint64)]
         handle.b200attn_workspace_bytes.restype = C.c_int
+        handle.b200attn_split_layout.argtypes = [C.c_int32] * 3 + [C.POINTER(C.c_int32)] * 3 + [C.c_int32]
+        handle.b200attn_split_layout.restype = C.c_int
         launch8 = [C.c_void_p] * 4 + [C.c_int] * 3 + [C.c_void_p]
         handle.b200attn_bhld_launch.argtypes = launch8
         handle.b200attn_bhld_launch.restype = C.c_int
@@ -159,6 +162,16 @@ def device_check(device: int = -1) -> None:
 
         ops.drop_workspaces()
     check(status)
+
+
+def split_layout(work_items: int, kv_tiles: int, sm_count: int = 148):
+    """(grid, cuts) of the tile-stream split of a dense call, or (0, []) if it would not be split:
+    CTA c of the first len(cuts) - 1 takes units [cuts[c], cuts[c + 1]) of the last round's
+    (item, K/V tile) pairs. Host arithmetic only."""
+    grid, runs = C.c_int32(0), C.c_int32(0)
+    cuts = (C.c_int32 * 256)()
+    check(lib().b200attn_split_layout(work_items, kv_tiles, sm_count, C.byref(grid), C.byref(runs), cuts, 256))
+    return grid.value, list(cuts[: runs.value + 1]) if grid.value else []
 
 
 def launch_count() -> int:

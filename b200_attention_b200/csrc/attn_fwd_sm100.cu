@@ -427,36 +427,25 @@ __device__ __forceinline__ int item_tiles(const FwdParams& p, int row0) {
 // whole item and CTA c takes items c, c + grid, c + 2 * grid, ... With splitting, the full rounds
 // are dealt the same way (all CTAs then stream the K/V of the same few heads at the same time,
 // which is what keeps K/V in L2), and only the items of the last, partly filled round are treated
-// differently (and taken first, see PieceWalk::take): the sequence of their (item, tile) pairs, item-major, is cut into one contiguous
-// run per CTA of near-equal length, so every CTA gets the same amount of tensor work whatever
-// items % grid is. A CTA's run is a (possibly cut) first item, whole items, and a (possibly cut)
-// last item. A run boundary that would leave a piece shorter than kSplitMinPieceTiles snaps to the
-// item boundary. Every role of a CTA walks the same pieces in the same order.
-// (Units are counted in 32 bits: the host only splits launches with fewer than 2^31 of them.)
+// differently (and taken first, see PieceWalk::take): the sequence of their (item, tile) pairs,
+// item-major, is cut into one contiguous run per CTA of near-equal length, so every CTA gets the
+// same amount of tensor work whatever items % grid is. A CTA's run is a (possibly cut) first item,
+// whole items, and a (possibly cut) last item. The host chooses the cuts (split_fill_cuts) such
+// that no piece is shorter than kSplitMinPieceTiles and hands them over in the parameters. Every
+// role of a CTA walks the same pieces in the same order.
 __device__ __forceinline__ int split_first_item(const FwdParams& p, int grid) {
   return (p.total_items / grid) * grid;  // items before this one belong to full rounds
 }
-// How many CTAs (the first ones) share the last round's items is the host's choice: every run is
-// at least kSplitMinPieceTiles long, so a run that lies strictly inside an item is never empty.
-__device__ __forceinline__ int split_runs(const FwdParams& p, int /*grid*/) { return p.split_runs; }
-// First unit of CTA c's run; units number the (item, tile) pairs of the last round's items.
-__device__ __forceinline__ int split_cut(const FwdParams& p, int c, int grid) {
-  const long long total = static_cast<long long>(p.total_items - split_first_item(p, grid)) * p.kv_tiles;
-  const int runs = split_runs(p, grid);
-  if (c >= runs) return int(total);
-  int u = int(total * c / runs);
-  const int r = u % p.kv_tiles;
-  if (r < kSplitMinPieceTiles) u -= r;
-  else if (p.kv_tiles - r < kSplitMinPieceTiles) u += p.kv_tiles - r;
-  return u;
+// First unit of CTA c's run; CTAs past the last run get the number of units (an empty run).
+__device__ __forceinline__ int split_cut(const FwdParams& p, int c) {
+  return p.split_cut[c < p.split_runs ? c : p.split_runs];
 }
-// The CTA whose run holds unit u.
-__device__ __forceinline__ int split_owner(const FwdParams& p, int u, int grid) {
-  const long long total = static_cast<long long>(p.total_items - split_first_item(p, grid)) * p.kv_tiles;
-  const int runs = split_runs(p, grid);
-  int c = int(static_cast<long long>(u) * runs / total);
-  while (c + 1 < runs && split_cut(p, c + 1, grid) <= u) ++c;
-  while (c > 0 && split_cut(p, c, grid) > u) --c;
+// The CTA whose run holds unit u (runs that lie inside an item are never empty).
+__device__ __forceinline__ int split_owner(const FwdParams& p, int u) {
+  const int runs = p.split_runs;
+  int c = int(static_cast<long long>(u) * runs / p.split_cut[runs]);
+  while (c + 1 < runs && p.split_cut[c + 1] <= u) ++c;
+  while (c > 0 && p.split_cut[c] > u) --c;
   return c;
 }
 
@@ -509,8 +498,8 @@ struct PieceWalk<true> {
 __device__ __forceinline__ void plan_run(const FwdParams& p, WsAux* aux) {
   const int grid = int(gridDim.x);
   const int whole_items = split_first_item(p, grid);
-  int u = split_cut(p, int(blockIdx.x), grid);
-  const int u_end = split_cut(p, int(blockIdx.x) + 1, grid);
+  int u = split_cut(p, int(blockIdx.x));
+  const int u_end = split_cut(p, int(blockIdx.x) + 1);
   int n = 0;
   while (u < u_end && n < kMaxRunPieces) {
     const int k = u / p.kv_tiles;
@@ -1059,8 +1048,8 @@ __device__ void split_merge_rows(const FwdParams& p, const Piece& pc, const Item
   const int grid = int(gridDim.x);
   const int T = p.kv_tiles;
   const int item_u0 = (pc.item - split_first_item(p, grid)) * T;
-  const int c_first = split_owner(p, item_u0, grid);
-  const int c_last = split_owner(p, item_u0 + T - 1, grid);
+  const int c_first = split_owner(p, item_u0);
+  const int c_last = split_owner(p, item_u0 + T - 1);
   const int pieces = c_last - c_first + 1;
 
   // every lane's stores are ordered before the ticket
@@ -1074,7 +1063,7 @@ __device__ void split_merge_rows(const FwdParams& p, const Piece& pc, const Item
   if (lane == 0) *ticket = 0;  // ready for the next launch
   __threadfence();
 
-  const int first_which = split_cut(p, c_first, grid) < item_u0 ? 1 : 0;
+  const int first_which = split_cut(p, c_first) < item_u0 ? 1 : 0;
   const float* slot0 = p.split_scratch + (size_t(c_first) * 2 + first_which) * kSplitSlotFloats;
   auto slot_of = [&](int k) -> const float* {  // k-th piece of the item
     return k == 0 ? slot0 : p.split_scratch + size_t(c_first + k) * 2 * kSplitSlotFloats;
@@ -1175,7 +1164,7 @@ __device__ void ws_epilogue_role(const FwdParams& p, WsAux* aux, uint32_t bar0, 
         // this piece covers only part of the item's keys: leave a partial in this CTA's slot
         // (slot 0 if the piece opens the CTA's run, else slot 1)
         const int unit = (item - split_first_item(p, int(gridDim.x))) * p.kv_tiles + pc.t0;
-        const bool opens_run = unit == split_cut(p, int(blockIdx.x), int(gridDim.x));
+        const bool opens_run = unit == split_cut(p, int(blockIdx.x));
         float* slot = p.split_scratch + (size_t(blockIdx.x) * 2 + (opens_run ? 0 : 1)) * kSplitSlotFloats;
         const int rs = q * kBlockM + r;
         out.valid = row < p.len_q;
@@ -1515,6 +1504,7 @@ SplitPlan split_plan(const FwdParams& p, int sm_count) {
   const long long tail_units = static_cast<long long>(tail_items) * p.kv_tiles;
   long long runs = tail_units / kSplitMinPieceTiles;
   if (runs > sm_count) runs = sm_count;
+  if (runs > kSplitMaxRuns) runs = kSplitMaxRuns;
   // Without full rounds behind it the merge of a cut item stands at the end of the launch, and it
   // costs about six tile periods per piece: keep the pieces per item few.
   constexpr int kExposedPiecesPerItem = 4, kMergeTilesPerPiece = 6;
@@ -1531,6 +1521,35 @@ SplitPlan split_plan(const FwdParams& p, int sm_count) {
   const long long split = static_cast<long long>(p.total_items / sm_count) * p.kv_tiles + (tail_units + runs - 1) / runs +
                           3 + (full_rounds ? 0 : kMergeTilesPerPiece * pieces_per_item);
   return (split * 100 < legacy * 97) ? SplitPlan{grid, int(runs)} : none;
+}
+
+// The cuts: run c ends where an even share of what is left would end, moved down to the nearest
+// admissible place (an item boundary, or at least kSplitMinPieceTiles away from both ends of the
+// item), so no run grows beyond the even share by more than the rounding and the slack spreads over
+// the runs that follow; a run is at least kSplitMinPieceTiles long.
+void split_fill_cuts(FwdParams& p, int sm_count, const SplitPlan& plan) {
+  const int T = p.kv_tiles;
+  const int total = (p.total_items % sm_count) * T;
+  const int runs = plan.runs < kSplitMaxRuns ? plan.runs : kSplitMaxRuns;
+  auto admissible = [&](int u) {
+    const int r = u % T;
+    return r == 0 || (r >= kSplitMinPieceTiles && r <= T - kSplitMinPieceTiles);
+  };
+  p.split_runs = runs;
+  p.split_cut[0] = 0;
+  for (int c = 0; c < runs; ++c) {
+    const int from = p.split_cut[c], left = runs - c;
+    int u = total;
+    if (left > 1 && from < total) {
+      int lowest = from + kSplitMinPieceTiles;
+      while (!admissible(lowest)) ++lowest;
+      u = from + (total - from + left - 1) / left;
+      while (u > lowest && !admissible(u)) --u;
+      if (u < lowest) u = lowest;
+      if (total - u < kSplitMinPieceTiles) u = total;
+    }
+    p.split_cut[c + 1] = u;
+  }
 }
 
 cudaError_t launch_fwd_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,

@@ -37,6 +37,8 @@ struct PartialState {
   int32_t emit;    // 1: store the (merged) partial to (o, lse) instead of the bf16 output
 };
 
+constexpr int kSplitMaxRuns = 160;  // runs of a tile-stream split (one per CTA): B200 has 148 SMs
+
 struct FwdParams {
   __nv_bfloat16* o;
   float* lse;  // [batch, heads, len_q] fp32 natural-log LSE, may be null
@@ -59,6 +61,9 @@ struct FwdParams {
   float* split_scratch;    // 2 slots of kSplitSlotFloats per CTA
   int32_t* split_tickets;  // kSplitTicketsPerCta counters per CTA, zero between launches
   int32_t split_runs;      // how many CTAs (the first ones) share the last round's items
+  // first unit of each of those CTAs' runs and, at [split_runs], the number of units; units number
+  // the (item, K/V tile) pairs of the last round's items, item-major (see split_fill_cuts)
+  int32_t split_cut[kSplitMaxRuns + 1];
   long long* trace;  // clock64 samples for timeline studies; used only by B200ATTN_TRACE builds
 };
 
@@ -67,7 +72,7 @@ struct FwdParams {
 // [256], and one arrival counter per (Q tile, epilogue warp).
 constexpr int kSplitSlotFloats = kItemRows * (kHeadDim + 1);
 constexpr int kSplitTicketsPerCta = kQTilesPerItem * 4;
-constexpr int kSplitMinPieceTiles = 4;  // a run boundary closer than this to an item boundary snaps to it
+constexpr int kSplitMinPieceTiles = 4;  // no piece of a cut item is shorter than this
 constexpr size_t split_workspace_bytes(int ctas) {
   return size_t(ctas) * (2 * size_t(kSplitSlotFloats) * sizeof(float) + kSplitTicketsPerCta * sizeof(int32_t));
 }
@@ -81,6 +86,8 @@ struct SplitPlan {
   int grid, runs;
 };
 SplitPlan split_plan(const FwdParams& p, int sm_count);
+// Writes p.split_runs and p.split_cut for a plan with grid > 0.
+void split_fill_cuts(FwdParams& p, int sm_count, const SplitPlan& plan);
 cudaError_t launch_fwd_serial(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                               const FwdParams& p, cudaStream_t stream);
 

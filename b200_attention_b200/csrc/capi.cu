@@ -310,7 +310,7 @@ int b200attn_forward(const b200attn_forward_args* a) {
       return fail(B200ATTN_ERR_INVALID_ARGUMENT, "workspace is smaller than b200attn_workspace_bytes()");
     const SplitPlan plan = split_plan(p, st->sm_count);
     if (plan.grid > 0) {
-      p.split_runs = plan.runs;
+      split_fill_cuts(p, st->sm_count, plan);
       p.split_scratch = static_cast<float*>(a->workspace);
       p.split_tickets = reinterpret_cast<int32_t*>(static_cast<char*>(a->workspace) +
                                                    size_t(st->sm_count) * 2 * kSplitSlotFloats * sizeof(float));
@@ -341,6 +341,27 @@ int b200attn_workspace_bytes(uint64_t* bytes) {
   const int rc = get_device(&device, &st);
   if (rc != 0) return rc;
   *bytes = split_workspace_bytes(st->sm_count);
+  return B200ATTN_OK;
+}
+
+int b200attn_split_layout(int32_t work_items, int32_t kv_tiles, int32_t sm_count, int32_t* grid,
+                          int32_t* runs, int32_t* cuts, int32_t max_cuts) {
+  if (grid == nullptr || runs == nullptr || work_items < 1 || kv_tiles < 1 || sm_count < 1)
+    return fail(B200ATTN_ERR_INVALID_ARGUMENT, "work_items, kv_tiles and sm_count must be positive, grid and runs non-null");
+  FwdParams p;
+  memset(&p, 0, sizeof p);
+  p.total_items = work_items;
+  p.kv_tiles = kv_tiles;
+  const SplitPlan plan = split_plan(p, sm_count);
+  *grid = plan.grid;
+  *runs = 0;
+  if (plan.grid == 0) return B200ATTN_OK;
+  split_fill_cuts(p, sm_count, plan);
+  *runs = p.split_runs;
+  if (cuts != nullptr) {
+    if (max_cuts < p.split_runs + 1) return fail(B200ATTN_ERR_INVALID_ARGUMENT, "cuts holds fewer than runs + 1 entries");
+    memcpy(cuts, p.split_cut, sizeof(int32_t) * size_t(p.split_runs + 1));
+  }
   return B200ATTN_OK;
 }
 

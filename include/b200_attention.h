@@ -117,6 +117,15 @@ B200ATTN_API int b200attn_forward(const b200attn_forward_args* args);
 /* Size of b200attn_forward_args.workspace for the current device (depends on its SM count). */
 B200ATTN_API int b200attn_workspace_bytes(uint64_t* bytes);
 
+/* How a dense, unmasked call of `work_items` 256-row work items (batch * heads * ceil(len_q / 256))
+ * over `kv_tiles` K/V tiles (ceil(len_kv / 128)) would be laid out on `sm_count` SMs when given a
+ * workspace; host arithmetic only, needs no device (no counterpart in the reference). *grid = CTAs
+ * launched, 0 if the call would not be split (then *runs = 0). Otherwise the first *runs CTAs share
+ * the items of the last, partly filled round: numbering that round's (item, tile) pairs item-major,
+ * CTA c works on units [cuts[c], cuts[c + 1]); cuts (may be NULL) receives *runs + 1 entries. */
+B200ATTN_API int b200attn_split_layout(int32_t work_items, int32_t kv_tiles, int32_t sm_count, int32_t* grid,
+                                       int32_t* runs, int32_t* cuts, int32_t max_cuts);
+
 /* Q [batch_heads, len_q, 128], K/V [batch_heads, len_kv, 128], O like Q; all contiguous bf16.
  * Unlike the reference launcher there is no len_q % 256 / len_kv % 128 restriction. */
 B200ATTN_API int b200attn_bhld_launch(const void* q, const void* k, const void* v, void* o, int batch_heads,

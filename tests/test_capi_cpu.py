@@ -152,3 +152,42 @@ def test_reference_side_launcher_bindings_compile_and_link(native_built, tmp_pat
     so = B.build(native_built["core"], tmp_path)
     lib = C.CDLL(str(so))
     assert hasattr(lib, B.BHLD_SYMBOL) and hasattr(lib, B.BSHD_SYMBOL)
+
+
+def test_split_layout_invariants():
+    """The host-side cuts of the tile-stream split: the runs cover the last round's units exactly,
+    empty runs only trail, no piece of a cut item is shorter than four tiles, and no run exceeds
+    the even share by more than a snap."""
+    import random
+
+    from b200_attention_b200 import _native as N
+
+    rng = random.Random(5)
+    cases = [(256, 64, 148), (512, 64, 148), (300, 9, 148), (149, 8, 148), (2, 130, 148), (100, 64, 148)]
+    cases += [(rng.randint(1, 1200), rng.randint(1, 300), rng.choice([148, 132, 160, 16])) for _ in range(3000)]
+    split = 0
+    for items, tiles, sms in cases:
+        grid, cuts = N.split_layout(items, tiles, sms)
+        if grid == 0:
+            assert cuts == []
+            continue
+        split += 1
+        total = (items % sms) * tiles
+        runs = len(cuts) - 1
+        assert grid == (sms if items >= sms else runs) and 1 <= runs <= sms
+        assert cuts[0] == 0 and cuts[-1] == total
+        lengths = [b - a for a, b in zip(cuts, cuts[1:])]
+        assert min(lengths) >= 0
+        first_empty = lengths.index(0) if 0 in lengths else runs
+        assert all(n == 0 for n in lengths[first_empty:]) and all(n >= 4 for n in lengths[:first_empty])
+        for a, b in zip(cuts, cuts[1:]):
+            u = a
+            while u < b:
+                end = min(b, (u // tiles + 1) * tiles)
+                assert end - u >= 4 or end - u == tiles, (items, tiles, sms, a, b)
+                u = end
+        assert max(lengths) <= -(-total // runs) + 4
+    assert split > 300
+    assert N.split_layout(256, 64, 148)[0] == 148
+    _, cuts = N.split_layout(256, 64, 148)
+    assert max(b - a for a, b in zip(cuts, cuts[1:])) == 47  # 108 items x 64 tiles over 148 runs: 46.7 each
