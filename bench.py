@@ -458,12 +458,14 @@ def configs_block(torch, ops, dev, stream, peaks, launches=10):
             theirs = k18_call(torch, q, k, v, layout)
             arms = {"ours": ours} if theirs is None else {"ours": ours, "k18": theirs}
             times = {arm: [] for arm in arms}
-            torch.cuda.synchronize(dev)
-            time.sleep(0.3)   # every configuration starts from the same short idle
             for order in (("ours", "k18"), ("k18", "ours")):   # each arm once first, once second
                 for arm in order:
                     if arm not in arms:
                         continue
+                    # every arm starts from the same short idle: without it the arm that runs last
+                    # in a row of four inherits the others' heat and falls off the boost clock first
+                    torch.cuda.synchronize(dev)
+                    time.sleep(0.25)
                     for _ in range(3):
                         arms[arm]()
                     total, _, _ = time_launches(torch, arms[arm], launches, stream)
