@@ -550,14 +550,16 @@ def run_ours(args, rank, local_rank, world):
     _native.device_check()
     launches0 = _native.launch_count()
     barrier()
-    total_ms, per_launch, burst_mhz = time_launches(torch, step, args.steps, stream, smclock, per_launch=True)
+    # one event before the first launch and one after the last: an event between two launches
+    # would keep the second from starting the moment the first ends
+    total_ms, _, burst_mhz = time_launches(torch, step, args.steps, stream, smclock)
     launches = _native.launch_count() - launches0
     barrier()
     _native.device_check()
+    kernel_ms = total_ms / args.steps   # this rank's own time per step
     total_ms = max_over_ranks(total_ms)
     ms_per_step = total_ms / args.steps
     value = job_flops / (ms_per_step * 1e-3) / 1e12
-    kernel_ms = statistics.mean(per_launch)
     achieved = rank_flops / (kernel_ms * 1e-3) / 1e12
     burst = regime(total_ms, args.steps, job_flops, burst_mhz)
     if args.only_timed:
