@@ -66,6 +66,7 @@ WORKLOADS = {
     "main": (4, 16, 8192, 8192, "bhld"),          # B=4 H=16 L=8192: the headline config
     "main_weak": (4, 16, 8192, 8192, "bhld"),     # one copy of it per GPU
     "main_bshd": (4, 16, 8192, 8192, "bshd"),
+    "main_rank8": (1, 8, 8192, 8192, "bhld"),     # what one of 8 GPUs owns of the headline problem
     "l1k": (64, 16, 1024, 1024, "bhld"),
     "l2k": (32, 16, 2048, 2048, "bhld"),
     "l4k": (16, 16, 4096, 4096, "bhld"),
@@ -323,6 +324,7 @@ def workload_config(name, world):
     kv = f", {opts['heads_kv']} K/V heads" if "heads_kv" in opts else ""
     split = name == "main" and world > 1
     weak = name != "main" and world > 1
+    input_bytes = (b * h * lq + 2 * b * opts.get("heads_kv", h) * lk) * HEAD_DIM * 2 // (world if split else 1)
     where = (f"GLOBAL B={b}, its {b * h} (batch, head) slices dealt to {world} GPUs" if split
              else f"B={b} per GPU" if weak else f"B={b}")
     return {"workload": f"{name}: dense {kind} attention forward, {where}, H={h}{kv}, Lq={lq}, "
@@ -331,14 +333,49 @@ def workload_config(name, world):
             "causal": bool(opts.get("causal", False)), "len_q": lq, "len_kv": lk, "head_dim": HEAD_DIM,
             "layout": layout,
             "parallelism": (f"(batch,head)-sharded x{world}, no collective" if world > 1 else "single GPU"),
-            "l2_policy": "inputs+outputs per step (Q,K,V,O) exceed the 126 MB L2; no flush"}
+            "l2_policy": l2_policy_text(input_bytes)}
 
 
 # --------------------------------------------------------------------------------------------
 # timing helpers (device side)
 # --------------------------------------------------------------------------------------------
-def time_launches(torch, call, n, stream, smclock=None, per_launch=False):
-    """n back-to-back calls on `stream`; returns (total_ms, [per-launch ms] or None, sm_mhz)."""
+L2_BYTES = 126e6
+FLUSH_BYTES = 256 << 20
+
+
+def flush_buffer_for(torch, dev, input_bytes):
+    """Inputs that fit the L2 would be served from it by the second launch on: such workloads get
+    a buffer twice the L2's size that is rewritten before every timed launch. None otherwise."""
+    if input_bytes > L2_BYTES:
+        return None
+    return torch.empty(FLUSH_BYTES, dtype=torch.uint8, device=dev)
+
+
+def l2_policy_text(input_bytes):
+    if input_bytes > L2_BYTES:
+        return f"inputs per step (Q,K,V: {input_bytes / 1e6:.0f} MB) exceed the 126 MB L2; no flush"
+    return (f"inputs per step (Q,K,V: {input_bytes / 1e6:.0f} MB) fit the 126 MB L2: a {FLUSH_BYTES >> 20} MiB buffer "
+            "is rewritten before every timed launch, outside the launch's own pair of events")
+
+
+def time_launches(torch, call, n, stream, smclock=None, per_launch=False, flush=None):
+    """n calls on `stream`; returns (total_ms, [per-launch ms] or None, sm_mhz). Back to back
+    between two events; with a `flush` buffer every call has its own pair of events, the buffer
+    is rewritten between the pairs and the total is the sum over the pairs."""
+    if flush is not None:
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        if smclock is not None:
+            smclock.before(stream)
+        for a, b in pairs:
+            flush.zero_()
+            a.record(stream)
+            call()
+            b.record(stream)
+        if smclock is not None:
+            smclock.after(stream)
+        stream.synchronize()
+        each = [a.elapsed_time(b) for a, b in pairs]
+        return sum(each), (each if per_launch else None), (smclock.mhz() if smclock is not None else None)
     evs = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1 if per_launch else 2)]
     if smclock is not None:
         smclock.before(stream)
@@ -366,12 +403,12 @@ def regime(total_ms, n, step_flops, mhz):
     return out
 
 
-def sustained_region(torch, call, est_ms, stream, smclock, warm_s=0.5, timed_s=1.0):
+def sustained_region(torch, call, est_ms, stream, smclock, warm_s=0.5, timed_s=1.0, flush=None):
     warm = max(3, int(warm_s * 1e3 / max(est_ms, 1e-3)) + 1)
     n = max(10, int(timed_s * 1e3 / max(est_ms, 1e-3)) + 1)
     for _ in range(warm):
         call()
-    total, _, mhz = time_launches(torch, call, n, stream, smclock)
+    total, _, mhz = time_launches(torch, call, n, stream, smclock, flush=flush)
     return total, n, mhz
 
 
@@ -455,6 +492,7 @@ def configs_block(torch, ops, dev, stream, peaks, launches=10):
                 ops.attention(q, k, v, layout=layout, out=o)
 
             fl = flops(b, h, lq, lk)
+            flush = flush_buffer_for(torch, dev, (q.numel() + 2 * k.numel()) * 2)
             theirs = k18_call(torch, q, k, v, layout)
             arms = {"ours": ours} if theirs is None else {"ours": ours, "k18": theirs}
             times = {arm: [] for arm in arms}
@@ -468,7 +506,7 @@ def configs_block(torch, ops, dev, stream, peaks, launches=10):
                     time.sleep(0.25)
                     for _ in range(3):
                         arms[arm]()
-                    total, _, _ = time_launches(torch, arms[arm], launches, stream)
+                    total, _, _ = time_launches(torch, arms[arm], launches, stream, flush=flush)
                     times[arm].append(total / launches)
             ms = statistics.mean(times["ours"])
             entry = {"tflops": fl / (ms * 1e-3) / 1e12, "ms": ms}
@@ -479,9 +517,11 @@ def configs_block(torch, ops, dev, stream, peaks, launches=10):
             if theirs is not None:
                 entry["k18_tflops"] = fl / (statistics.mean(times["k18"]) * 1e-3) / 1e12
                 entry["ratio_to_k18"] = entry["tflops"] / entry["k18_tflops"]
+            if flush is not None:
+                entry["l2_flushed"] = True
             out[f"{name}_{layout}"] = {k_: (round(v_, 3) if isinstance(v_, float) else v_)
                                        for k_, v_ in entry.items()}
-            del q, k, v, o, theirs
+            del q, k, v, o, theirs, flush
             torch.cuda.empty_cache()
     return out
 
@@ -539,6 +579,10 @@ def run_ours(args, rank, local_rank, world):
         sharding.run_shard(q, k, v, ranges, out=o)
 
     step = shard if split else whole
+    # a rank whose inputs fit the L2 rewrites a larger buffer before every timed launch
+    rank_units = sharding.units_of(ranges) if split else b * h
+    rank_input_bytes = (rank_units * lq + 2 * (rank_units * hk // h) * lk) * HEAD_DIM * 2
+    flush = flush_buffer_for(torch, dev, rank_input_bytes)
     # FLOPs of one step on this rank and of one step of the whole job
     rank_flops = flops(sharding.units_of(ranges), 1, lq, lk) if split else flops(b, h, lq, lk, causal)
     job_flops = flops(b, h, lq, lk, causal) * (1 if split or world == 1 else world)
@@ -552,7 +596,7 @@ def run_ours(args, rank, local_rank, world):
     barrier()
     # one event before the first launch and one after the last: an event between two launches
     # would keep the second from starting the moment the first ends
-    total_ms, _, burst_mhz = time_launches(torch, step, args.steps, stream, smclock)
+    total_ms, _, burst_mhz = time_launches(torch, step, args.steps, stream, smclock, flush=flush)
     launches = _native.launch_count() - launches0
     barrier()
     _native.device_check()
@@ -589,7 +633,7 @@ def run_ours(args, rank, local_rank, world):
         step()
     barrier()
     n_sus = max(10, int(args.sustain_s * 1e3 / max(ms_per_step, 1e-3)) + 1)
-    sus_ms, _, sus_mhz = time_launches(torch, step, n_sus, stream, smclock)
+    sus_ms, _, sus_mhz = time_launches(torch, step, n_sus, stream, smclock, flush=flush)
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     _native.device_check()
