@@ -331,11 +331,6 @@ __device__ __forceinline__ float row_max(const uint32_t (&s)[4][32]) {
 #define B200ATTN_REBASE_LOG2 32.0f
 #endif
 
-#ifdef B200ATTN_MMA_HINTS
-#define B200ATTN_UNLIKELY(x) __builtin_expect(!!(x), 0)
-#else
-#define B200ATTN_UNLIKELY(x) (x)
-#endif
 constexpr int kPairSlots = 2;                 // ring of (V, K) pairs
 constexpr int kPairBytes = 2 * kTileBytes;    // V tile, then K tile
 constexpr int kWsThreads = 512;
@@ -795,7 +790,7 @@ __device__ void ws_mma_role(const FwdParams& p, const WsAux* aux, uint32_t smem_
         const uint32_t o_tmem = tmem_base + kQTilesPerItem * kBlockN + q * kHeadDim;
         PROF_LAP(0);
         if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 0);
-        if (B200ATTN_UNLIKELY(i == 0)) {
+        if (i == 0) {
           // the previous item's epilogue must have read O_q out before it is overwritten
           if (!(ok = w.wait_issue(bar(kBarOFree + q), o_free_parity, 240 + q))) break;
         }
@@ -806,7 +801,7 @@ __device__ void ws_mma_role(const FwdParams& p, const WsAux* aux, uint32_t smem_
         issue_pv(lead, o_tmem, s_tmem, v_smem, /*accumulate=*/i > 0);
         PROF_LAP(4);
         if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 2);
-        if (B200ATTN_UNLIKELY(!has_next)) {
+        if (!has_next) {
           umma_commit_lead(lead, bar(kBarPvDone + q));
         } else {
           if (lead) B200ATTN_TRACE_EVENT(p, 2, item, i, q, 3);
@@ -948,13 +943,8 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
         tail = true;
         valid = min(valid, row_limit - i * kBlockN + 1);
       }
-#ifdef B200ATTN_EXPECT_NO_TAIL
-      if (__builtin_expect(tail || i == 0, 0)) tmem_wait_ld();  // these paths look at all chunks at once
-      if (__builtin_expect(tail, 0)) mask_tail(s, valid);
-#else
       if (tail || i == 0) tmem_wait_ld();  // these paths look at all chunks at once
       if (tail) mask_tail(s, valid);
-#endif
 
       uint32_t packed[4][16];
       f2 sum_a = f2_splat(0.0f), sum_b = f2_splat(0.0f);
