@@ -380,8 +380,9 @@ struct ItemCoord {
 // Work items are numbered (batch, head)-major, so consecutive items share K/V in L2. With a causal
 // mask items differ in length (2 .. 2 * m_blocks tiles), so they are dealt longest first: heads are
 // taken in groups of kCausalHeadGroup (K/V of a group, and of the next one starting, fit in L2),
-// and inside a group the query block index falls slowest and the head changes fastest, so the
-// round-robin assignment hands every CTA nearly the same multiset of lengths.
+// and inside a group the query block index falls (in every other group: rises) slowest and the
+// head changes fastest, so the round-robin assignment hands every CTA nearly the same multiset of
+// lengths.
 constexpr int kCausalHeadGroup = 8;
 template <bool kCausal>
 __device__ __forceinline__ ItemCoord decode_item(const FwdParams& p, int item) {
@@ -390,8 +391,12 @@ __device__ __forceinline__ ItemCoord decode_item(const FwdParams& p, int item) {
   if (kCausal) {
     const int per_group = kCausalHeadGroup * p.m_blocks;
     const int group = item / per_group;
-    const int idx = item - group * per_group;
+    int idx = item - group * per_group;
     const int heads_here = min(kCausalHeadGroup, p.batch * p.heads - group * kCausalHeadGroup);
+    // every other group is dealt shortest first: a CTA that got the long items of one group gets
+    // the short ones of the next, which evens out the sums (11 % -> 4 % above the mean at B4 H16
+    // L8192 on 148 CTAs)
+    if (group & 1) idx = heads_here * p.m_blocks - 1 - idx;
     const int mb_rev = idx / heads_here;
     bh = group * kCausalHeadGroup + (idx - mb_rev * heads_here);
     mb = p.m_blocks - 1 - mb_rev;
