@@ -378,27 +378,33 @@ struct ItemCoord {
 };
 
 // Work items are numbered (batch, head)-major, so consecutive items share K/V in L2. With a causal
-// mask items differ in length (2 .. 2 * m_blocks tiles), so they are dealt longest first: heads are
-// taken in groups of kCausalHeadGroup (K/V of a group, and of the next one starting, fit in L2),
-// and inside a group the query block index falls (in every other group: rises) slowest and the
-// head changes fastest, so the round-robin assignment hands every CTA nearly the same multiset of
-// lengths.
-constexpr int kCausalHeadGroup = 8;
+// mask items differ in length (2 .. 2 * m_blocks tiles). Their numbers then mean something else:
+// heads are taken in groups (the K/V of a group fit in L2, or enough CTAs work on each head at a
+// time to share its tiles there), and inside a group the items are numbered by falling length,
+// query block index slowest and head fastest. CausalWalk deals these numbers to the CTAs.
+// K/V heads per group: as many as keep the group's K and V within 64 MiB, but at least 16 (with
+// 148 CTAs on 16 heads, nine CTAs stream each head's tiles at about the same time and share them
+// in L2 even where the group as a whole does not fit).
+#ifndef B200ATTN_CAUSAL_GROUP
+#define B200ATTN_CAUSAL_GROUP 16
+#endif
+__device__ __forceinline__ int causal_group_heads(const FwdParams& p) {
+  const int fit = (64 << 20) / (2 * kHeadDim * 2) / p.len_kv;  // K and V rows of 256 bytes each
+  // whole sets of query heads that share a K/V head
+  return max(B200ATTN_CAUSAL_GROUP, fit) * p.kv_group;
+}
 template <bool kCausal>
 __device__ __forceinline__ ItemCoord decode_item(const FwdParams& p, int item) {
   ItemCoord c;
   int bh, mb;
   if (kCausal) {
-    const int per_group = kCausalHeadGroup * p.m_blocks;
+    const int group_heads = causal_group_heads(p);
+    const int per_group = group_heads * p.m_blocks;
     const int group = item / per_group;
-    int idx = item - group * per_group;
-    const int heads_here = min(kCausalHeadGroup, p.batch * p.heads - group * kCausalHeadGroup);
-    // every other group is dealt shortest first: a CTA that got the long items of one group gets
-    // the short ones of the next, which evens out the sums (11 % -> 4 % above the mean at B4 H16
-    // L8192 on 148 CTAs)
-    if (group & 1) idx = heads_here * p.m_blocks - 1 - idx;
+    const int idx = item - group * per_group;
+    const int heads_here = min(group_heads, p.batch * p.heads - group * group_heads);
     const int mb_rev = idx / heads_here;
-    bh = group * kCausalHeadGroup + (idx - mb_rev * heads_here);
+    bh = group * group_heads + (idx - mb_rev * heads_here);
     mb = p.m_blocks - 1 - mb_rev;
   } else {
     bh = item / p.m_blocks;
@@ -499,6 +505,49 @@ struct PieceWalk<true> {
   }
 };
 
+// With a causal mask: the groups of heads one after the other; a group's items (numbered by
+// falling length, see decode_item) are dealt in rounds of one item per CTA, back and forth: in
+// every other round the CTAs take theirs in reverse order, and every other group takes the CTAs
+// themselves in reverse order, so whoever drew long items draws short ones next and the sums even
+// out (busiest CTA 1.6 % above the mean at B4 H16 L8192 on 148 CTAs; 11 % when every group is
+// simply dealt longest first).
+struct CausalWalk {
+  int g, r;  // head group, round inside the group
+  __device__ __forceinline__ CausalWalk(const FwdParams&, const WsAux*) : g(0), r(0) {}
+  __device__ __forceinline__ bool take(const FwdParams& p, Piece& out) {
+    const int grid = int(gridDim.x);
+    const int nbh = p.batch * p.heads;
+    const int group_heads = causal_group_heads(p);
+    while (g * group_heads < nbh) {
+      const int n = min(group_heads, nbh - g * group_heads) * p.m_blocks;  // items of the group
+      const int base = r * grid;
+      if (base < n) {
+        const int in_round = min(grid, n - base);
+        const int c = (g & 1) ? grid - 1 - int(blockIdx.x) : int(blockIdx.x);
+        if (c < in_round) {
+          out.item = g * group_heads * p.m_blocks + base + ((r & 1) ? in_round - 1 - c : c);
+          out.t0 = 0;
+          out.t1 = p.kv_tiles;
+          ++r;
+          return true;
+        }
+      }
+      ++g;
+      r = 0;
+    }
+    return false;
+  }
+};
+
+template <bool kCausal, bool kSplit>
+struct WalkOf {
+  using type = PieceWalk<kSplit>;
+};
+template <>
+struct WalkOf<true, false> {
+  using type = CausalWalk;
+};
+
 // Thread 0, before the roles start: this CTA's run through the last round, as pieces.
 __device__ __forceinline__ void plan_run(const FwdParams& p, WsAux* aux) {
   const int grid = int(gridDim.x);
@@ -570,7 +619,7 @@ __device__ void ws_load_role(const FwdParams& p, const WsAux* aux, const CUtenso
   };
 
   bool first = true;
-  PieceWalk<kSplit> pw(p, aux);
+  typename WalkOf<kCausal, kSplit>::type pw(p, aux);
   Piece pc;
   while (ok && pw.take(p, pc)) {
     const int item = pc.item;
@@ -604,7 +653,7 @@ __device__ void ws_load_role(const FwdParams& p, const WsAux* aux, const CUtenso
         ok = push_pair(true, (tb + i) * kBlockN, kvc, true, (tb + i + 1) * kBlockN, kvc, 111);
       } else {
         // the last V of this piece shares its pair with the first K of the CTA's next piece, if any
-        PieceWalk<kSplit> ahead = pw;
+        typename WalkOf<kCausal, kSplit>::type ahead = pw;
         Piece np;
         const bool has_next_piece = ahead.take(p, np);
         ItemCoord next_kvc = kvc;
@@ -648,7 +697,10 @@ __device__ void ws_mma_role_causal(const FwdParams& p, uint32_t smem_q, uint32_t
   bool ok = true;
   bool k_ready = false;
 
-  for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
+  CausalWalk pw(p, nullptr);
+  Piece pc;
+  while (ok && pw.take(p, pc)) {
+    const int item = pc.item;
     const int row0 = decode_item<true>(p, item).row0;
     int Tq[kQTilesPerItem];
 #pragma unroll
@@ -747,7 +799,7 @@ __device__ void ws_mma_role(const FwdParams& p, const WsAux* aux, uint32_t smem_
 
   PROF_DECL(8);  // 0 other, 1 wait pair, 3 wait P (+O_FREE), 4 issue PV, 5 issue QK, 6 commits
 
-  PieceWalk<kSplit> pw(p, aux);
+  typename WalkOf<kCausal, kSplit>::type pw(p, aux);
   Piece pc;
   while (ok && pw.take(p, pc)) {
     const int item = pc.item;
@@ -899,7 +951,7 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
   uint32_t fin_free_parity = 1;  // passes on the fresh barrier: nothing to consume yet
   PROF_DECL(8);  // 0 other, 1 wait S, 2 TMEM load, 3 exponentials + check, 4 store + signal
 
-  PieceWalk<kSplit> pw(p, aux);
+  typename WalkOf<kCausal, kSplit>::type pw(p, aux);
   Piece pc;
   while (pw.take(p, pc)) {
     const int item = pc.item;
@@ -1147,7 +1199,7 @@ __device__ void ws_epilogue_role(const FwdParams& p, WsAux* aux, uint32_t bar0, 
   const int r = warp_in_group * 32 + lane;
   uint32_t fin_parity = 0;
 
-  PieceWalk<kSplit> pw(p, aux);
+  typename WalkOf<kCausal, kSplit>::type pw(p, aux);
   Piece pc;
   while (pw.take(p, pc)) {
     const int item = pc.item;
