@@ -106,7 +106,7 @@ SEQUENCE_WORKLOADS = {
 NCU_TRAFFIC = {
     "main": (515.5e6, "profiles/attn_fwd_ws_kernel_main_B4_H16_L8192.md"),
     "dit_cross": (155.0e6, "profiles/attn_fwd_ws_kernel_dit_cross_B1_H12_Lq32768_Lk512.md"),
-    "causal": (659.0e6, "profiles/attn_fwd_ws_kernel_causal_B4_H16_L8192.md"),
+    "causal": (681.0e6, "profiles/attn_fwd_ws_kernel_causal_B4_H16_L8192.md"),
 }
 
 
