@@ -68,6 +68,12 @@ CAUSAL_SHAPES = [
     (1, 2, 2, 256, 1000),    # long history: every row sees at least 745 keys
     (3, 6, 3, 640, 640),     # odd counts, items of a head spread over CTAs
     (1, 32, 8, 4096, 4096),  # more work items than CTAs: the persistent loop walks mixed lengths
+    # 8192 keys make the head groups sixteen K/V heads wide, so these deal several groups, the
+    # odd ones with the CTAs in reverse order and the last one smaller than the rest (rounds taken
+    # back and forth inside a group: the full-size causal test, 512 items per group)
+    (1, 40, 40, 640, 8192),  # groups of 16, 16 and 8 heads, three items each
+    (1, 40, 20, 384, 8192),  # two query heads per K/V head: groups of 32 and 8 query heads
+    (2, 20, 20, 768, 8192),  # the same groups over two batch entries (a group spans both)
 ]
 
 
