@@ -505,6 +505,35 @@ struct PieceWalk<true> {
   }
 };
 
+// The same walk worked out from the launch parameters alone (the cuts sit in the constant bank, so
+// every value here is uniform across the warp as far as the compiler can see, which a value read
+// from shared memory is not): for the roles whose tile loop is the hot one.
+struct ParamPieceWalk {
+  int u, k;  // next unit of the run; whole items taken so far
+  __device__ __forceinline__ ParamPieceWalk(const FwdParams& p, const WsAux*)
+      : u(split_cut(p, int(blockIdx.x))), k(0) {}
+  __device__ __forceinline__ bool take(const FwdParams& p, Piece& out) {
+    const int grid = int(gridDim.x);
+    const int first = split_first_item(p, grid);
+    const int u_end = split_cut(p, int(blockIdx.x) + 1);
+    if (u < u_end) {
+      const int j = u / p.kv_tiles;
+      out.item = first + j;
+      out.t0 = u - j * p.kv_tiles;
+      out.t1 = min(p.kv_tiles, out.t0 + (u_end - u));
+      u += out.t1 - out.t0;
+      return true;
+    }
+    const int item = int(blockIdx.x) + k * grid;
+    if (item >= first) return false;
+    out.item = item;
+    out.t0 = 0;
+    out.t1 = p.kv_tiles;
+    ++k;
+    return true;
+  }
+};
+
 // With a causal mask: the groups of heads one after the other; a group's items (numbered by
 // falling length, see decode_item) are dealt in rounds of one item per CTA, back and forth: in
 // every other round the CTAs take theirs in reverse order, and every other group takes the CTAs
@@ -542,10 +571,17 @@ struct CausalWalk {
 template <bool kCausal, bool kSplit>
 struct WalkOf {
   using type = PieceWalk<kSplit>;
+  using hot = PieceWalk<kSplit>;
 };
 template <>
 struct WalkOf<true, false> {
   using type = CausalWalk;
+  using hot = CausalWalk;
+};
+template <>
+struct WalkOf<false, true> {
+  using type = PieceWalk<true>;  // the epilogue also looks the run's pieces up for the merges
+  using hot = ParamPieceWalk;
 };
 
 // Thread 0, before the roles start: this CTA's run through the last round, as pieces.
@@ -619,7 +655,7 @@ __device__ void ws_load_role(const FwdParams& p, const WsAux* aux, const CUtenso
   };
 
   bool first = true;
-  typename WalkOf<kCausal, kSplit>::type pw(p, aux);
+  typename WalkOf<kCausal, kSplit>::hot pw(p, aux);
   Piece pc;
   while (ok && pw.take(p, pc)) {
     const int item = pc.item;
@@ -653,7 +689,7 @@ __device__ void ws_load_role(const FwdParams& p, const WsAux* aux, const CUtenso
         ok = push_pair(true, (tb + i) * kBlockN, kvc, true, (tb + i + 1) * kBlockN, kvc, 111);
       } else {
         // the last V of this piece shares its pair with the first K of the CTA's next piece, if any
-        typename WalkOf<kCausal, kSplit>::type ahead = pw;
+        typename WalkOf<kCausal, kSplit>::hot ahead = pw;
         Piece np;
         const bool has_next_piece = ahead.take(p, np);
         ItemCoord next_kvc = kvc;
@@ -799,7 +835,7 @@ __device__ void ws_mma_role(const FwdParams& p, const WsAux* aux, uint32_t smem_
 
   PROF_DECL(8);  // 0 other, 1 wait pair, 3 wait P (+O_FREE), 4 issue PV, 5 issue QK, 6 commits
 
-  typename WalkOf<kCausal, kSplit>::type pw(p, aux);
+  typename WalkOf<kCausal, kSplit>::hot pw(p, aux);
   Piece pc;
   while (ok && pw.take(p, pc)) {
     const int item = pc.item;
@@ -951,7 +987,7 @@ __device__ void ws_softmax_role(const FwdParams& p, WsAux* aux, uint32_t bar0, u
   uint32_t fin_free_parity = 1;  // passes on the fresh barrier: nothing to consume yet
   PROF_DECL(8);  // 0 other, 1 wait S, 2 TMEM load, 3 exponentials + check, 4 store + signal
 
-  typename WalkOf<kCausal, kSplit>::type pw(p, aux);
+  typename WalkOf<kCausal, kSplit>::hot pw(p, aux);
   Piece pc;
   while (pw.take(p, pc)) {
     const int item = pc.item;
