@@ -2,7 +2,8 @@
 // accumulation, optional fp32 LSE, head_dim 128; optionally with a causal mask and with grouped
 // K/V heads.
 //
-// Two kernels share the operand layout, descriptors and epilogue:
+// Two kernels share the operand layout, descriptors and epilogue (attn_fwd_ws_short_kernel is the
+// first one's body again, launched for items of few K/V tiles):
 //
 //   attn_fwd_ws_kernel      the production kernel (a template on the causal mask and on how
 //                           work is dealt: whole 256-row work items round-robin, or with the
@@ -1298,11 +1299,10 @@ __device__ void ws_epilogue_role(const FwdParams& p, WsAux* aux, uint32_t bar0, 
   }
 }
 
-template <bool kCausal, bool kSplit>
-__global__ void __launch_bounds__(kWsThreads, 1)
-attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
-                   const __grid_constant__ CUtensorMap tmap_k,
-                   const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
+// kShortKv: the variant for items of few K/V tiles (see attn_fwd_ws_short_kernel).
+template <bool kCausal, bool kSplit, bool kShortKv>
+__device__ __forceinline__ void ws_kernel_body(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,
+                                               const CUtensorMap& tmap_v, const FwdParams& p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -1367,7 +1367,11 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
     reg_shrink<kRegsOther>();
     const uint32_t lead = (lane == 0) ? 1u : 0u;
     if (warp == 12) {
-      ws_mma_role<kCausal, kSplit>(p, aux, smem_q, smem_kv, bar0, tmem_base, lead, w);
+      // kShortKv: the TMEM base (read from shared memory above) goes through a warp-wide
+      // reduction first, whose result the compiler knows to be the same in every lane. Measured
+      // +2.1 % at 4 K/V tiles per item, +0.8 % at 8, -0.5 % at 64.
+      ws_mma_role<kCausal, kSplit>(p, aux, smem_q, smem_kv, bar0,
+                                   kShortKv ? __reduce_or_sync(0xffffffffu, tmem_base) : tmem_base, lead, w);
     } else if (warp == 13) {
       if (lead) {
         tma_prefetch_desc(&tmap_q);
@@ -1386,6 +1390,23 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
+}
+
+template <bool kCausal, bool kSplit>
+__global__ void __launch_bounds__(kWsThreads, 1)
+attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                   const __grid_constant__ CUtensorMap tmap_k,
+                   const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
+  ws_kernel_body<kCausal, kSplit, false>(tmap_q, tmap_k, tmap_v, p);
+}
+
+// The dense, unsplit kernel as launched for items of at most kShortKvTiles K/V tiles.
+constexpr int kShortKvTiles = 8;
+__global__ void __launch_bounds__(kWsThreads, 1)
+attn_fwd_ws_short_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                         const __grid_constant__ CUtensorMap tmap_k,
+                         const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
+  ws_kernel_body<false, false, true>(tmap_q, tmap_k, tmap_v, p);
 }
 
 // ==========================================================================================
@@ -1571,9 +1592,10 @@ cudaError_t prepare_kernels() {
   // blocks in hardware until the CTA's pool has room, so refuse to run unless the pool the
   // launch reserves (registers per thread x 512 threads) covers what the roles ask for.
   constexpr int kPoolNeeded = 128 * (2 * kRegsSoftmax + kRegsEpilogue + kRegsOther);
-  const void* ws_kernels[3] = {reinterpret_cast<const void*>(&attn_fwd_ws_kernel<false, false>),
+  const void* ws_kernels[4] = {reinterpret_cast<const void*>(&attn_fwd_ws_kernel<false, false>),
                                reinterpret_cast<const void*>(&attn_fwd_ws_kernel<true, false>),
-                               reinterpret_cast<const void*>(&attn_fwd_ws_kernel<false, true>)};
+                               reinterpret_cast<const void*>(&attn_fwd_ws_kernel<false, true>),
+                               reinterpret_cast<const void*>(&attn_fwd_ws_short_kernel)};
   for (const void* kernel : ws_kernels) {
     cudaFuncAttributes fa;
     cudaError_t e = cudaFuncGetAttributes(&fa, kernel);
@@ -1653,7 +1675,11 @@ cudaError_t launch_fwd_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CU
   } else if (p.split_scratch != nullptr) {
     attn_fwd_ws_kernel<false, true><<<split_plan(p, sm_count).grid, kWsThreads, kWsSmemBytes, stream>>>(tq, tk, tv, p);
   } else {
-    attn_fwd_ws_kernel<false, false><<<grid, kWsThreads, kWsSmemBytes, stream>>>(tq, tk, tv, p);
+    if (p.kv_tiles <= kShortKvTiles) {
+      attn_fwd_ws_short_kernel<<<grid, kWsThreads, kWsSmemBytes, stream>>>(tq, tk, tv, p);
+    } else {
+      attn_fwd_ws_kernel<false, false><<<grid, kWsThreads, kWsSmemBytes, stream>>>(tq, tk, tv, p);
+    }
   }
   return cudaGetLastError();
 }
